@@ -1,0 +1,146 @@
+/*
+ * flint_attn -- C ABI of the B200 (sm_100a) attention hot path of flint-mac.
+ *
+ * Shape and conventions follow the reference's engine interface, src/capi.h:10-37:
+ * an opaque handle created by *_open and freed only by *_close; `err` is a
+ * caller-owned buffer (may be NULL) that receives a NUL-terminated, truncated
+ * message; int32 status returns are 0 on success and -1 on failure; no C++
+ * exception crosses the boundary; a handle is single-owner and NOT thread-safe,
+ * the caller serialises calls (src/capi.h:1).  Host-buffer entry points are
+ * synchronous like the reference's (src/engine.mm:930); the *_dev variants take
+ * device pointers and a CUDA stream and return after enqueueing.
+ *
+ * What it replaces inside the reference engine: the two attention call sites,
+ *   decode : k_attn_dec + k_attn_combine     src/engine.mm:735-766, src/metal/fused.metal:254-350
+ *   prefill: k_qk_prefill + k_attn_prefill   src/engine.mm:1087-1104, src/metal/prefill.metal:100-266
+ * with the per-layer K/V caches of src/engine.mm:509-511 held by this library.
+ *
+ * Fixed shapes (src/metal/flint_config.h:10-31): 32 query heads, 4 KV heads, head dim 128,
+ * sliding window 513 keys (current token included), 1024-slot ring per SWA layer.
+ * One token's projections are passed as the reference's packed row
+ *   qkv[5120] = q[32][128] | k[4][128] | v[4][128]          (src/metal/fused.metal:211)
+ * before QK RMSNorm / RoPE; attention output rows are [32][128] = 4096 values.
+ */
+#ifndef FLINT_ATTN_H
+#define FLINT_ATTN_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct flint_attn flint_attn;
+
+/* Element types of the qkv input rows and of the attention output rows. */
+enum { FLINT_ATTN_F32 = 0, FLINT_ATTN_BF16 = 1 };
+
+enum {
+    FLINT_ATTN_N_HEAD = 32,
+    FLINT_ATTN_N_HEAD_KV = 4,
+    FLINT_ATTN_HEAD_DIM = 128,
+    FLINT_ATTN_QKV_DIM = 5120,
+    FLINT_ATTN_OUT_DIM = 4096,
+    FLINT_ATTN_PARTIAL_DIM = 130 /* acc[128], m, l  (src/metal/fused.metal:324-327) */
+};
+
+/* Counterpart of flint_config (src/capi.h:12-17): what the engine needs to know to allocate its KV caches. */
+typedef struct {
+    int32_t device;                /* CUDA device ordinal this handle lives on */
+    int32_t n_layers;              /* attention layers held */
+    const int32_t *layer_is_swa;   /* [n_layers] 1: 513-key window + 1024-slot ring; 0: full context (n_ctx slots) */
+    const int32_t *layer_has_rope; /* [n_layers] 1: NEOX RoPE on q and k (src/ref/ref_model.h:18 keeps both flags) */
+    int32_t max_seqs;              /* independent sequences resident on this device */
+    int32_t n_ctx;                 /* context length per sequence (src/capi.h:16) */
+    int32_t kv_rank;               /* KV-range sharding of full layers over devices: this shard ... */
+    int32_t kv_ranks;              /* ... of this many (0 or 1: not sharded) */
+} flint_attn_config;
+
+/* src/capi.h:20-21. NULL + message on failure. */
+flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err_len);
+void flint_attn_close(flint_attn *a);
+
+/* src/capi.h:23,25 (per sequence here: the reference is single-session). */
+int32_t flint_attn_n_ctx(const flint_attn *a);
+int32_t flint_attn_pos(const flint_attn *a, int32_t seq);
+
+/* src/capi.h:27-29, src/engine.h:60: move the sequence back to `pos` (<= current).  O(1); caches are not
+ * touched.  -1 if pos < 0 or pos > current (src/capi.mm:52-56).  After rolling back more than 511 tokens the
+ * caller must prefill again from max(0, pos-512) for the SWA rings to be right (server/src/main.rs:96-100);
+ * flint_attn_rollback_restart gives that position. */
+int32_t flint_attn_truncate(flint_attn *a, int32_t seq, int32_t pos);
+int32_t flint_attn_rollback_restart(int32_t cached_len, int32_t pos);
+
+/* Engine::step / Engine::prefill advance the position once per token after ALL layers ran
+ * (src/engine.mm:936, :1248).  Attention calls below read the position and do not move it. */
+int32_t flint_attn_advance(flint_attn *a, int32_t n, const int32_t *seqs, int32_t n_tokens);
+
+/* Per-layer learned parameters: blk.N.attn_q_norm / attn_k_norm [128], attn_sinks [32], fp32
+ * (bound at src/engine.mm:747-749).  Host pointers; copied. */
+int32_t flint_attn_set_layer(flint_attn *a, int32_t layer, const float *q_norm, const float *k_norm,
+                             const float *sinks, char *err, int32_t err_len);
+
+/* ---- decode: one new token for each of n sequences ---------------------------------------------
+ * Replaces k_attn_dec(args, qkv, q_norm, k_norm, sinks, k_cache, v_cache, out, partial) and k_attn_combine
+ * (src/metal/fused.metal:254-259, 332-334).  For sequence seqs[i] at position p = flint_attn_pos(seqs[i]):
+ * RMSNorm(+RoPE at p) of row i's q and k, K/V of the token rounded to half and written to slot p (p & 1023 on
+ * SWA layers), softmax over cached keys [max(0,p-512) or 0, p) plus the token itself plus the head's sink,
+ * split over the key range inside the GPU and merged.  qkv: [n][5120]; out: [n][4096]. */
+int32_t flint_attn_decode(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs, const void *qkv,
+                          int32_t qkv_dtype, void *out, int32_t out_dtype, char *err, int32_t err_len);
+int32_t flint_attn_decode_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs, const void *qkv_dev,
+                              int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
+                              int32_t err_len);
+
+/* KV-range sharded decode (kv_ranks > 1; full layers): this device's keys only, no sink.  partial_dev:
+ * [n][32][130] fp32 = un-normalised acc[128], max m (natural-log units), sum l per head -- the record of
+ * src/metal/fused.metal:324-327.  The shard that owns position p folds and stores the new token. */
+int32_t flint_attn_decode_partial_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs,
+                                      const void *qkv_dev, int32_t qkv_dtype, float *partial_dev, void *cuda_stream,
+                                      char *err, int32_t err_len);
+/* src/metal/fused.metal:332-350 over gathered shards: partials_dev [n_parts][n][32][130] -> out [n][4096];
+ * the sink enters here, once. */
+int32_t flint_attn_combine_dev(flint_attn *a, int32_t layer, int32_t n, int32_t n_parts, const float *partials_dev,
+                               void *out_dev, int32_t out_dtype, void *cuda_stream, char *err, int32_t err_len);
+
+/* ---- prefill: n_tok tokens of one sequence from its current position -----------------------------
+ * Replaces the chunk loop k_qk_prefill + k_attn_prefill (src/engine.mm:1080-1104, src/metal/prefill.metal:100-266):
+ * norm(+RoPE at p0+t), K/V to the cache (ring slot (p0+t) & 1023 on SWA layers), causal + window + sink flash
+ * attention.  qkv: [n_tok][5120]; out: [n_tok][4096]. */
+int32_t flint_attn_prefill(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv,
+                           int32_t qkv_dtype, void *out, int32_t out_dtype, char *err, int32_t err_len);
+int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv_dev,
+                               int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
+                               int32_t err_len);
+
+/* ---- cache access for tests and cache pre-loading (counterpart of the Engine::debug_* hooks, src/engine.h:37-47)
+ * Cache layout on the device, per layer: K and V separately, half [max_seqs][4][n_slots][128], n_slots = 1024
+ * (SWA) or the shard's share of n_ctx (full).  k/v host arrays here: [4][n][128] half bits for slots
+ * [slot0, slot0+n) of one sequence. */
+int32_t flint_attn_n_slots(const flint_attn *a, int32_t layer);
+int32_t flint_attn_read_kv(flint_attn *a, int32_t layer, int32_t seq, int32_t slot0, int32_t n, uint16_t *k,
+                           uint16_t *v, char *err, int32_t err_len);
+int32_t flint_attn_write_kv(flint_attn *a, int32_t layer, int32_t seq, int32_t slot0, int32_t n, const uint16_t *k,
+                            const uint16_t *v, char *err, int32_t err_len);
+/* Device addresses of a layer's K (which = 0) or V (1) cache, for zero-copy fills by a co-resident producer. */
+void *flint_attn_kv_dev(flint_attn *a, int32_t layer, int32_t which);
+/* Declare that a sequence's caches already hold `pos` tokens (after flint_attn_write_kv / a device-side fill). */
+int32_t flint_attn_set_pos(flint_attn *a, int32_t seq, int32_t pos);
+
+/* ---- host-side planning, exposed for tests (no GPU needed) -----------------------------------------
+ * The split-K work list the decode launch would use for n tokens at positions pos[]: one record of 8 int32 per
+ * work item = { token, kv_head, j0, j1, fold_new_token, split, n_split, first_partial }.  Cached keys [j0, j1)
+ * of the items of one (token, kv_head) tile [k_begin, pos) clipped to [kv_lo, kv_hi) exactly once; exactly one
+ * item per (token, kv_head) has fold_new_token = 1 when kv_lo <= pos < kv_hi.  Own policy (the reference's,
+ * src/engine.mm:742-743, is tuned for 32 splits on an M5).  Returns the item count, or -1 if cap is too small. */
+int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, int32_t kv_lo, int32_t kv_hi,
+                               int32_t target_items, int32_t *items, int32_t cap);
+/* Tuning knob: work items the planner aims for per launch (default: 4 waves of 2 CTAs on every SM). */
+int32_t flint_attn_set_target_items(flint_attn *a, int32_t target_items);
+/* Number of kernel launches this handle has enqueued so far. */
+int64_t flint_attn_launch_count(const flint_attn *a);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

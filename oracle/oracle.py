@@ -1,0 +1,227 @@
+"""ctypes binding of the CPU oracle (liboracle.so) -- TEST INFRASTRUCTURE ONLY.
+
+Imported by tests/, by the smoke check and by the benchmark's CPU-baseline leg; never by the
+shipped package.  Every function is a thin call into oracle/flint_attn_oracle.c, which restates
+the reference's src/ref/ref_model.cpp:45-61,107-149.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liboracle.so")
+
+N_HEAD, N_HEAD_KV, HEAD_DIM, GQA = 32, 4, 128, 8
+Q_DIM, KV_DIM, QKV_DIM = 4096, 512, 5120
+N_SWA, MAX_CHUNK, SWA_RING = 513, 512, 1024
+
+# Streams of the seeded generator: one per synthetic tensor kind.
+STREAM_QKV, STREAM_QNORM, STREAM_KNORM, STREAM_SINKS, STREAM_KCACHE, STREAM_VCACHE, STREAM_CTX = 1, 2, 3, 4, 5, 6, 7
+
+
+def build(force: bool = False) -> str:
+    """Compile liboracle.so with the Makefile beside this file (gcc, a second or two)."""
+    src = os.path.join(HERE, "flint_attn_oracle.c")
+    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", HERE, "liboracle.so"], check=True, capture_output=True)
+    return LIB_PATH
+
+
+_lib = None
+_f32p = np.ctypeslib.ndpointer(np.float32, flags="C_CONTIGUOUS")
+_u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
+_i32p = np.ctypeslib.ndpointer(np.int32, flags="C_CONTIGUOUS")
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(LIB_PATH)
+        L.fo_gen_normal.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_float, C.c_float, _f32p]
+        L.fo_gen_u64.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64]
+        L.fo_gen_u64.restype = C.c_uint64
+        L.fo_round_f16.argtypes = [_f32p, C.c_uint64]
+        L.fo_round_bf16.argtypes = [_f32p, C.c_uint64]
+        L.fo_f32_to_f16_bits.argtypes = [_f32p, _u16p, C.c_uint64]
+        L.fo_f16_bits_to_f32.argtypes = [_u16p, _f32p, C.c_uint64]
+        L.fo_f32_to_bf16_bits.argtypes = [_f32p, _u16p, C.c_uint64]
+        L.fo_bf16_bits_to_f32.argtypes = [_u16p, _f32p, C.c_uint64]
+        L.fo_rmsnorm.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_float]
+        L.fo_rope_neox.argtypes = [_f32p, C.c_int, C.c_int, C.c_float]
+        L.fo_inv_freq.argtypes = [C.c_float, _f32p]
+        L.fo_qk_norm_rope.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int]
+        L.fo_attend.argtypes = [_f32p, _f32p, _f32p, _f32p, C.c_int, C.c_int, _f32p, C.c_int]
+        L.fo_layer_forward.argtypes = [_f32p, C.c_int, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int,
+                                       _f32p, _f32p, _f32p, C.c_int]
+        L.fo_decode_token_f16cache.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, _u16p, _u16p,
+                                               C.c_int64, _f32p, C.c_int]
+        L.fo_attend_partial.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, _f32p]
+        L.fo_combine.argtypes = [_f32p, C.c_int, _f32p, _f32p]
+        L.fo_slot.argtypes = [C.c_int32, C.c_int]
+        L.fo_slot.restype = C.c_int32
+        L.fo_k_begin.argtypes = [C.c_int32, C.c_int]
+        L.fo_k_begin.restype = C.c_int32
+        L.fo_ref_split_policy.argtypes = [C.c_int32, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+        L.fo_rollback_restart.argtypes = [C.c_int32, C.c_int32]
+        L.fo_rollback_restart.restype = C.c_int32
+        L.fo_ring_owners.argtypes = [C.c_int32, _i32p]
+        _lib = L
+    return _lib
+
+
+# ---------------------------------------------------------------- generator and conversions
+def gen_normal(seed: int, stream: int, n: int, mean: float = 0.0, std: float = 1.0, first: int = 0) -> np.ndarray:
+    out = np.empty(n, np.float32)
+    lib().fo_gen_normal(seed, stream, first, n, mean, std, out)
+    return out
+
+
+def gen_u64(seed: int, stream: int, index: int) -> int:
+    return int(lib().fo_gen_u64(seed, stream, index))
+
+
+def round_f16(x: np.ndarray) -> np.ndarray:
+    y = np.ascontiguousarray(x, np.float32).copy()
+    lib().fo_round_f16(y.reshape(-1), y.size)
+    return y
+
+
+def round_bf16(x: np.ndarray) -> np.ndarray:
+    y = np.ascontiguousarray(x, np.float32).copy()
+    lib().fo_round_bf16(y.reshape(-1), y.size)
+    return y
+
+
+def to_f16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    lib().fo_f32_to_f16_bits(x.reshape(-1), out.reshape(-1), x.size)
+    return out
+
+
+def from_f16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.uint16)
+    out = np.empty(x.shape, np.float32)
+    lib().fo_f16_bits_to_f32(x.reshape(-1), out.reshape(-1), x.size)
+    return out
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    lib().fo_f32_to_bf16_bits(x.reshape(-1), out.reshape(-1), x.size)
+    return out
+
+
+def from_bf16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.uint16)
+    out = np.empty(x.shape, np.float32)
+    lib().fo_bf16_bits_to_f32(x.reshape(-1), out.reshape(-1), x.size)
+    return out
+
+
+# ---------------------------------------------------------------- synthetic layer parameters
+def layer_weights(seed: int, layer: int = 0):
+    """q_norm, k_norm ~ 1 + N(0, 0.1) [128]; sinks ~ N(0, 1) [32] (the shapes of blk.N.attn_{q,k}_norm / attn_sinks)."""
+    qn = gen_normal(seed, STREAM_QNORM + 16 * layer, HEAD_DIM, 1.0, 0.1)
+    kn = gen_normal(seed, STREAM_KNORM + 16 * layer, HEAD_DIM, 1.0, 0.1)
+    sk = gen_normal(seed, STREAM_SINKS + 16 * layer, N_HEAD, 0.0, 1.0)
+    return qn, kn, sk
+
+
+def raw_qkv(seed: int, layer: int, first_pos: int, n_tok: int, seq: int = 0) -> np.ndarray:
+    """Raw (pre-norm) q|k|v rows [n_tok][5120] ~ N(0,1) of positions first_pos.. of sequence `seq`."""
+    stream = STREAM_QKV + 16 * layer + 4096 * seq
+    return gen_normal(seed, stream, n_tok * QKV_DIM, first=first_pos * QKV_DIM).reshape(n_tok, QKV_DIM)
+
+
+# ---------------------------------------------------------------- arithmetic
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float = 1e-6) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty_like(x)
+    lib().fo_rmsnorm(x, np.ascontiguousarray(w, np.float32), y, x.size, eps)
+    return y
+
+
+def inv_freq(theta: float = 10000.0) -> np.ndarray:
+    out = np.empty(64, np.float32)
+    lib().fo_inv_freq(theta, out)
+    return out
+
+
+def qk_norm_rope(qkv_row: np.ndarray, qn, kn, pos: int, has_rope: bool) -> np.ndarray:
+    row = np.ascontiguousarray(qkv_row, np.float32).copy()
+    lib().fo_qk_norm_rope(row, qn, kn, pos, int(has_rope))
+    return row
+
+
+def layer_forward(qkv: np.ndarray, qn, kn, sinks, is_swa: bool, has_rope: bool, round_kv_f16: bool = False,
+                  p0: int = 0, kc: np.ndarray | None = None, vc: np.ndarray | None = None, n_threads: int = 1):
+    """Token-by-token attention of one layer. Returns (att [T][4096], kc, vc) with kc/vc [p0+T][512] fp32."""
+    qkv = np.ascontiguousarray(qkv, np.float32)
+    T = qkv.shape[0]
+    kfull = np.zeros((p0 + T, KV_DIM), np.float32)
+    vfull = np.zeros((p0 + T, KV_DIM), np.float32)
+    if p0:
+        kfull[:p0] = kc[:p0]
+        vfull[:p0] = vc[:p0]
+    att = np.empty((T, Q_DIM), np.float32)
+    lib().fo_layer_forward(qkv.reshape(-1), T, p0, qn, kn, sinks, int(is_swa), int(has_rope), int(round_kv_f16),
+                           kfull.reshape(-1), vfull.reshape(-1), att.reshape(-1), n_threads)
+    return att, kfull, vfull
+
+
+def decode_token_f16cache(qkv_row, pos: int, qn, kn, sinks, is_swa: bool, has_rope: bool, k16: np.ndarray,
+                          v16: np.ndarray, n_threads: int = 1) -> np.ndarray:
+    """k16/v16: uint16 half bits [4][n_slots][128] of one sequence; updated in place with the new token."""
+    assert k16.dtype == np.uint16 and k16.flags.c_contiguous and v16.flags.c_contiguous
+    n_slots = k16.shape[1]
+    att = np.empty(Q_DIM, np.float32)
+    lib().fo_decode_token_f16cache(np.ascontiguousarray(qkv_row, np.float32), pos, qn, kn, sinks, int(is_swa),
+                                   int(has_rope), k16.reshape(-1), v16.reshape(-1), n_slots, att, n_threads)
+    return att
+
+
+def attend_partial(q, kc, vc, j0: int, j1: int) -> np.ndarray:
+    part = np.empty((N_HEAD, HEAD_DIM + 2), np.float32)
+    lib().fo_attend_partial(np.ascontiguousarray(q, np.float32).reshape(-1), kc.reshape(-1), vc.reshape(-1), j0, j1,
+                            part.reshape(-1))
+    return part
+
+
+def combine(part: np.ndarray, sinks) -> np.ndarray:
+    """part [32][n_split][130] -> out [32][128]."""
+    part = np.ascontiguousarray(part, np.float32)
+    out = np.empty((N_HEAD, HEAD_DIM), np.float32)
+    lib().fo_combine(part.reshape(-1), part.shape[1], sinks, out.reshape(-1))
+    return out
+
+
+# ---------------------------------------------------------------- integer maps
+def slot(pos: int, is_swa: bool) -> int:
+    return int(lib().fo_slot(pos, int(is_swa)))
+
+
+def k_begin(pos: int, is_swa: bool) -> int:
+    return int(lib().fo_k_begin(pos, int(is_swa)))
+
+
+def ref_split_policy(pos: int, is_swa: bool):
+    a, b = C.c_int32(), C.c_int32()
+    lib().fo_ref_split_policy(pos, int(is_swa), C.byref(a), C.byref(b))
+    return a.value, b.value
+
+
+def rollback_restart(cached_len: int, p: int) -> int:
+    return int(lib().fo_rollback_restart(cached_len, p))
+
+
+def ring_owners(n: int) -> np.ndarray:
+    out = np.empty(SWA_RING, np.int32)
+    lib().fo_ring_owners(n, out)
+    return out
