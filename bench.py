@@ -1,0 +1,331 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|longctx]
+
+Default workload (`decode`) is the batched decode configuration: per GPU 64 independent sequences with 8192
+cached tokens each on one full-attention layer, Q/K/V rows bf16, fp16 KV cache, RMSNorm + RoPE + KV write fused in.
+One step = one decode-attention pass over the whole batch, positions advancing by one each step.  Sequences are
+independent, so with N GPUs every rank holds its own 64 sequences (weak scaling) and there is no collective on
+the data path.  One JSON line is printed by rank 0.
+
+`--impl reference` times the CPU restatement of the reference's src/ref attention (the oracle) on the host cores
+for the same configuration, on a bounded sample of sequences.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B_PER_GPU, CTX, QKV_DIM, OUT_DIM = 64, 8192, 5120, 4096
+KV_BYTES_PER_KEY = 2048  # K + V, 4 KV heads x 128 dims x fp16, each read once per GQA group
+PREFILL_T = 4000
+
+
+def decode_bytes(n_seq: int, n_cached: int) -> int:
+    """Algorithmic HBM bytes of one decode step: cached K/V once per KV head, q|k|v row in (bf16),
+    new K/V written (fp16), output row out (bf16)."""
+    return n_seq * (KV_BYTES_PER_KEY * n_cached + QKV_DIM * 2 + 2 * 512 * 2 + OUT_DIM * 2)
+
+
+def prefill_flops(n_tok: int, window: int = 513) -> int:
+    """4 * 128 * 32 * sum_p min(p+1, window): QK^T and PV over the causal band only."""
+    p = np.arange(n_tok, dtype=np.int64)
+    return int(4 * 128 * 32 * np.minimum(p + 1, window).sum())
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx, self.rows, self._stop, self._t = gpu_index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                r = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                    "-i", str(self.idx)], capture_output=True, text=True, timeout=5)
+                if r.returncode == 0 and r.stdout.strip():
+                    self.rows.append([x.strip() for x in r.stdout.strip().split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=10)
+
+    def summary(self):
+        sm, mx, reasons = [], 0.0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def dist_setup(n_gpus: int):
+    import torch
+
+    rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world):
+    import torch
+
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch
+    import torch.distributed as dist
+
+    t = torch.tensor([x], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def as_tensor(torch, ptr, numel, dtype):
+    """torch view (no copy) of device memory owned by the library."""
+    class H:
+        pass
+
+    h = H()
+    h.__cuda_array_interface__ = {"shape": (numel * torch.empty((), dtype=dtype).element_size(),), "typestr": "|u1",
+                                  "data": (ptr, False), "version": 3}
+    return torch.as_tensor(h, device="cuda").view(dtype)
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+def cpu_decode_sample(seed: int, n_sample: int, n_cached: int, n_threads: int, reps: int = 1):
+    """The oracle (src/ref arithmetic) on n_sample sequences of the decode workload; returns seconds per sequence-token."""
+    from oracle import oracle as fo
+
+    w = fo.layer_weights(seed, 0)
+    rng = np.random.default_rng(seed)
+    times = []
+    for s in range(n_sample):
+        k16 = fo.to_f16_bits(rng.standard_normal((4, n_cached + 1, 128), dtype=np.float32))
+        v16 = fo.to_f16_bits(rng.standard_normal((4, n_cached + 1, 128), dtype=np.float32))
+        row = fo.round_bf16(rng.standard_normal(QKV_DIM, dtype=np.float32))
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fo.decode_token_f16cache(row, n_cached, *w, False, True, k16, v16, n_threads=n_threads)
+            times.append(time.perf_counter() - t0)
+    return float(np.mean(times))
+
+
+def run_reference(args):
+    """The reference's CPU attention (oracle port) for the decode workload on all host cores, bounded sample per step."""
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    n_sample = 4
+    for _ in range(args.warmup):
+        cpu_decode_sample(0, 1, CTX, cores)
+    t0 = time.perf_counter()
+    per_seq = []
+    for k in range(args.steps):
+        per_seq.append(cpu_decode_sample(k + 1, n_sample, CTX, cores))
+    wall = time.perf_counter() - t0
+    sec_per_seq = float(np.mean(per_seq))
+    gbs = decode_bytes(1, CTX) / sec_per_seq / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_per_seq * B_PER_GPU * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "decode: 64 seqs x 8192 cached tokens, 1 full layer, 32q/4kv heads x 128",
+                   "timed_sample": f"{n_sample} sequences per step, scaled to 64"},
+        "tok_per_s": 1.0 / sec_per_seq,
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"{n_sample} of 64 sequences per step x {args.steps} steps, OpenMP over heads"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_s": wall,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+def run_decode(args):
+    import torch
+
+    import flint_mac_b200 as fa
+
+    rank, world, local = dist_setup(args.gpus)
+    hbm_peak, _, peak_kind = measured_peaks()
+    total_steps = args.warmup + args.steps
+    n_ctx = CTX + 2 * total_steps + 8
+    h = fa.Attn([False], [True], B_PER_GPU, n_ctx, device=local)
+    from oracle import oracle as fo  # seeded layer parameters only; the oracle is not on the measured path
+
+    h.set_layer(0, *fo.layer_weights(0, 0))
+    n_slots = h.n_slots(0)
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    for which in (0, 1):
+        as_tensor(torch, h.kv_dev(0, which), B_PER_GPU * 4 * n_slots * 128, torch.float16).normal_(generator=gen)
+    seqs = list(range(B_PER_GPU))
+    qkv = torch.randn(total_steps, B_PER_GPU, QKV_DIM, generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.empty(B_PER_GPU, OUT_DIM, device="cuda", dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def reset():
+        for s in seqs:
+            h.set_pos(s, CTX)
+
+    def step(i):
+        h.decode_dev(0, seqs, qkv[i], fa.BF16, out, fa.BF16, stream)
+        h.advance(seqs, 1)
+
+    # ---- device-resident throughput ("value")
+    reset()
+    for i in range(args.warmup):
+        step(i)
+    barrier(world)
+    h.set_timing(True)
+    launches0 = h.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        ev1.record()
+        barrier(world)
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1), world)
+    kernel_ms, n_timed = h.kernel_ms()
+    h.set_timing(False)
+    launches = h.launch_count() - launches0
+    step_bytes = sum(decode_bytes(B_PER_GPU, CTX + args.warmup + i) for i in range(args.steps)) / args.steps
+    ms_per_step = ms_total / args.steps
+    value = step_bytes * world / (ms_per_step * 1e-3) / 1e9
+    kernel_ms_avg = kernel_ms / max(n_timed, 1)
+    achieved = step_bytes / (kernel_ms_avg * 1e-3) / 1e9
+
+    # ---- end to end through the host-buffer entry point: pinned host rows in, host rows out, every step
+    reset()
+    qkv_host = qkv.cpu().pin_memory()
+    out_host = torch.empty(B_PER_GPU, OUT_DIM, dtype=torch.bfloat16).pin_memory()
+    for i in range(args.warmup):
+        h.decode(0, seqs, qkv_host[i], fa.BF16, out_host, fa.BF16)
+        h.advance(seqs, 1)
+    barrier(world)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        h.decode(0, seqs, qkv_host[args.warmup + i], fa.BF16, out_host, fa.BF16)
+        h.advance(seqs, 1)
+    barrier(world)
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world) / args.steps
+    e2e_value = step_bytes * world / (e2e_ms * 1e-3) / 1e9
+    checksum = float(out_host.float().abs().mean())
+
+    line = None
+    if rank == 0:
+        cores = os.cpu_count() or 1
+        t_cpu0 = time.perf_counter()
+        sec_per_seq = cpu_decode_sample(0, 4, CTX, cores, reps=2)
+        cpu_gbs = decode_bytes(1, CTX) / sec_per_seq / 1e9
+        line = {
+            "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 KV, f16 tensor-core products, f32 accumulate/softmax", "data": "synthetic",
+            "config": {"workload": "decode: 64 seqs/GPU x 8192 cached tokens, 1 full layer, 32q/4kv heads x 128, "
+                                   "bf16 qkv rows, fp16 KV cache, norm+RoPE+KV write fused",
+                       "seqs_per_gpu": B_PER_GPU, "cached_tokens": CTX, "sharding": "independent sequences per GPU",
+                       "l2": "inputs larger than L2 (1 GiB of KV per GPU per step)"},
+            "tok_per_s": B_PER_GPU * world / (ms_per_step * 1e-3),
+            "pct_of_hbm_peak": 100.0 * value / world / hbm_peak,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "kernel": "k_decode_attn", "kernel_us": kernel_ms_avg * 1e3, "bytes_per_launch": step_bytes},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": B_PER_GPU * QKV_DIM * 2, "d2h_bytes_per_step": B_PER_GPU * OUT_DIM * 2,
+                    "tok_per_s": B_PER_GPU * world / (e2e_ms * 1e-3), "checksum": checksum},
+            "gpu_launches": launches,
+            "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                             "sample": "4 of 64 sequences x 2 repeats of the same step, OpenMP over heads",
+                             "tok_per_s": 1.0 / sec_per_seq, "wall_s": time.perf_counter() - t_cpu0},
+            "clocks": clk.summary(),
+        }
+    h.close()
+    return line, rank, world
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    line, rank, world = run_decode(args)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,6 @@
+"""B200-native attention hot path of flint-mac: sm_100a CUDA kernels behind a C ABI (include/flint_attn.h).
+
+The Python here is only a ctypes mirror of that ABI, in the role the reference's server/src/ffi.rs plays for
+src/capi.h.  There is no CPU fallback: without the compiled library, or without a B200, calls fail loudly.
+"""
+from .capi import Attn, FlintAttnError, load_library, F32, BF16, plan_decode, rollback_restart  # noqa: F401

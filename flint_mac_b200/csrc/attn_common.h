@@ -1,0 +1,72 @@
+// Types shared by the host launcher and the sm_100a attention kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace flint {
+
+// Fixed model shape (the reference's src/metal/flint_config.h:10-31).
+constexpr int kNHead = 32;
+constexpr int kNHeadKv = 4;
+constexpr int kHeadDim = 128;
+constexpr int kGqa = 8;
+constexpr int kQDim = kNHead * kHeadDim;       // 4096
+constexpr int kKvDim = kNHeadKv * kHeadDim;    // 512
+constexpr int kQkvDim = kQDim + 2 * kKvDim;    // 5120
+constexpr int kNSwa = 513;                     // window, current token included
+constexpr int kSwaRing = 1024;
+constexpr float kRmsEps = 1e-6f;
+constexpr float kRopeTheta = 10000.0f;
+constexpr int kPartialDim = kHeadDim + 2;      // acc[128], m, l
+
+constexpr int kDtypeF32 = 0;
+constexpr int kDtypeBf16 = 1;
+
+// One unit of decode work: the 8 query heads of one KV head of one token against cached keys [j0, j1).
+struct DecItem {
+    int32_t tok;       // row of this call's qkv / out
+    int32_t seq;       // sequence index into the caches
+    int32_t kvh;       // KV head 0..3
+    int32_t pos;       // position of the new token
+    int32_t j0, j1;    // cached key positions covered by this item
+    int32_t fold;      // 1: also attends to the new token itself and stores its K/V
+    int32_t split;     // index of this item among the n_split items of its (tok, kvh) group
+    int32_t n_split;
+    int32_t part0;     // first partial record of the group in the scratch buffer
+    int32_t group;     // ticket counter index
+    int32_t pad;
+};
+static_assert(sizeof(DecItem) == 48, "DecItem is uploaded as raw bytes");
+
+struct DecParams {
+    const DecItem *items;
+    const void *qkv;        // [n][5120] fp32 or bf16
+    void *out;              // [n][4096] fp32 or bf16 (mode 0)
+    float *partial_out;     // [n][32][130] (mode 1: this device's keys only, no sink)
+    const float *q_norm, *k_norm, *sinks, *inv_freq;
+    __half *k_cache, *v_cache;  // [max_seqs][4][n_slots][128]
+    float *scratch;         // split-K partial records [..][8][130]
+    int *tickets;           // one counter per (tok, kvh) group, zero between launches
+    long long seq_stride;   // halves between consecutive sequences = 4 * n_slots * 128
+    int n_slots;
+    uint32_t slot_mask;     // 1023 on ring layers, 0xFFFFFFFF otherwise
+    int kv_lo;              // position held by slot 0 of a (sharded) full layer
+    int has_rope;
+    int qkv_dtype, out_dtype;
+    int mode;               // 0: final output with sink; 1: partial record output
+};
+
+struct CombineParams {
+    const float *partials;  // [n_parts][n][32][130]
+    const float *sinks;
+    void *out;              // [n][4096]
+    int n, n_parts, out_dtype;
+};
+
+cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream);
+cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream);
+cudaError_t decode_kernel_setup();  // opt-in shared memory size; once per device
+
+}  // namespace flint

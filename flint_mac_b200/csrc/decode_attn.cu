@@ -1,0 +1,371 @@
+// Fused decode attention for sm_100a.
+//
+// Replaces the reference's k_attn_dec + k_attn_combine (src/metal/fused.metal:254-350).  Same semantics:
+// QK RMSNorm, NEOX RoPE, K/V of the new token rounded to half and written to its cache slot, online softmax over
+// the cached keys of a split, the learned per-head sink added exactly once in the final merge.
+//
+// Different shape, chosen for B200.  One CTA works on one (token, KV head, key range) item and serves all 8 query
+// heads of the GQA group from a single pass over K and V, so every cache byte leaves HBM once (the reference
+// re-reads it once per query head and relies on its cache).  K/V rows stream through a 3-stage cp.async pipeline
+// of 64-key tiles into XOR-swizzled shared memory.  Scores are computed transposed on the tensor cores,
+// S^T[16 keys x 8 heads] = K[16 x 128] . Q^T[128 x 8] with mma.m16n8k16 (N = 8 is exactly the GQA group, so no
+// padding work), probabilities are transposed in registers with movmatrix and O^T[128 dims x 8 heads] +=
+// V^T . P^T.  Softmax statistics stay in fp32 and are reduced with warp shuffles.  The four warps of a CTA take
+// 16 keys each of every tile and keep private (m, l, O) state, merged once at the end through shared memory like
+// the reference's four simdgroups (fused.metal:301-318).  Splits of one (token, KV head) group write fp32 partial
+// records {acc[128], m, l} (fused.metal:324-327); the last CTA of the group to finish (atomic ticket) merges them,
+// so there is no second launch and no spin-wait anywhere.
+#include "attn_common.h"
+#include "ptx.cuh"
+
+namespace flint {
+
+namespace {
+
+constexpr int kTileKeys = 64;
+constexpr int kStages = 3;
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kRowBytes = kHeadDim * 2;             // 256
+constexpr int kTileBytes = kTileKeys * kRowBytes;   // 16 KiB per K or V tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct __align__(16) DecSmem {
+    unsigned char k[kStages][kTileBytes];
+    unsigned char v[kStages][kTileBytes];
+    __half q[kGqa][kHeadDim];   // normalised, rotated, pre-scaled query heads of the group
+    __half knew[kHeadDim];      // the new token's K (after norm/RoPE) and V as stored in the cache
+    __half vnew[kHeadDim];
+    float red_m[kWarps][kGqa];
+    float red_l[kWarps][kGqa];
+    int is_last;
+};
+// The per-warp output accumulators are merged through the (by then idle) K tiles.
+static_assert(sizeof(float) * kWarps * kGqa * kHeadDim <= kStages * kTileBytes, "merge buffer aliases the K tiles");
+
+__device__ __forceinline__ float4 load_row4(const void *base, int dtype, size_t elem0, int lane) {
+    if (dtype == kDtypeF32) return reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem0)[lane];
+    const uint2 u = reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + elem0)[lane];
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&u.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+
+// One 128-wide head row spread over a warp, lane owning dims 4*lane..4*lane+3: RMSNorm with weight, then NEOX RoPE
+// pairing dim i with i+64, i.e. lane with lane^16 (same arithmetic as src/ref/ref_model.cpp:45-61).
+__device__ __forceinline__ float4 norm_rope(float4 v, const float *w, const float *inv_freq, int lane, int pos,
+                                            bool rope) {
+    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps);
+    const float4 wv = reinterpret_cast<const float4 *>(w)[lane];
+    v.x = v.x * scale * wv.x;
+    v.y = v.y * scale * wv.y;
+    v.z = v.z * scale * wv.z;
+    v.w = v.w * scale * wv.w;
+    if (!rope) return v;
+    float x[4] = {v.x, v.y, v.z, v.w}, out[4];
+    const float4 fr = reinterpret_cast<const float4 *>(inv_freq)[lane & 15];
+    const float freq[4] = {fr.x, fr.y, fr.z, fr.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float partner = __shfl_xor_sync(0xffffffffu, x[j], 16);
+        float s, c;
+        sincosf(float(pos) * freq[j], &s, &c);
+        out[j] = lane < 16 ? x[j] * c - partner * s : partner * s + x[j] * c;
+    }
+    return make_float4(out[0], out[1], out[2], out[3]);
+}
+
+__device__ __forceinline__ void store_half4(__half *dst, float4 v) {
+    const uint2 u = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+    *reinterpret_cast<uint2 *>(dst) = u;
+}
+
+__device__ __forceinline__ void store_out(void *out, int dtype, size_t idx, float v) {
+    if (dtype == kDtypeF32) static_cast<float *>(out)[idx] = v;
+    else static_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
+}
+
+__global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    DecSmem &sm = *reinterpret_cast<DecSmem *>(smem_raw);
+
+    const DecItem it = p.items[blockIdx.x];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int j0 = it.j0, j1 = it.j1;
+    const int j_end = j1 + (it.fold ? 1 : 0);  // the new token sits right after the cached range of a fold item
+    const int n_tiles = (j_end - j0 + kTileKeys - 1) / kTileKeys;
+
+    const __half *kbase = p.k_cache + size_t(it.seq) * p.seq_stride + size_t(it.kvh) * p.n_slots * kHeadDim;
+    const __half *vbase = p.v_cache + size_t(it.seq) * p.seq_stride + size_t(it.kvh) * p.n_slots * kHeadDim;
+    const uint32_t ks_addr = smem_u32(&sm.k[0][0]), vs_addr = smem_u32(&sm.v[0][0]);
+
+    auto load_tile = [&](int t) {
+        const int stage = t % kStages;
+        const int jt = j0 + t * kTileKeys;
+#pragma unroll
+        for (int i = 0; i < (kTileKeys * 16) / kThreads; i++) {
+            const int c = tid + kThreads * i;
+            const int row = c >> 4, ch = c & 15;
+            const int j = jt + row;
+            const bool valid = j < j1;  // cached keys only; other rows are zero-filled
+            const int slot = valid ? int(uint32_t(j) & p.slot_mask) - p.kv_lo : 0;
+            const size_t off = size_t(slot) * kHeadDim + ch * 8;
+            const uint32_t dst = stage * kTileBytes + row * kRowBytes + ((ch ^ (row & 7)) << 4);
+            cp_async16(ks_addr + dst, kbase + off, valid ? 16u : 0u);
+            cp_async16(vs_addr + dst, vbase + off, valid ? 16u : 0u);
+        }
+    };
+
+    // Start the first tiles before the query prologue so their latency overlaps it.
+#pragma unroll
+    for (int t = 0; t < kStages - 1; t++) {
+        if (t < n_tiles) load_tile(t);
+        cp_async_commit();
+    }
+
+    // ---- prologue: q heads of the group (and the new token's k, v) -> shared memory --------------------------
+    {
+        const size_t row0 = size_t(it.tok) * kQkvDim;
+        const float qscale = rsqrtf(float(kHeadDim)) * kLog2e;  // softmax runs in base 2
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int hl = warp * 2 + i;  // head within the group
+            float4 q = load_row4(p.qkv, p.qkv_dtype, row0 + size_t(it.kvh * kGqa + hl) * kHeadDim, lane);
+            q = norm_rope(q, p.q_norm, p.inv_freq, lane, it.pos, p.has_rope != 0);
+            q.x *= qscale; q.y *= qscale; q.z *= qscale; q.w *= qscale;
+            store_half4(&sm.q[hl][4 * lane], q);
+        }
+        if (it.fold) {
+            if (warp == 0) {
+                float4 k = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + size_t(it.kvh) * kHeadDim, lane);
+                k = norm_rope(k, p.k_norm, p.inv_freq, lane, it.pos, p.has_rope != 0);
+                store_half4(&sm.knew[4 * lane], k);
+                const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
+                store_half4(const_cast<__half *>(kbase) + size_t(slot) * kHeadDim + 4 * lane, k);
+            } else if (warp == 1) {
+                const float4 v = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + kKvDim + size_t(it.kvh) * kHeadDim, lane);
+                store_half4(&sm.vnew[4 * lane], v);
+                const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
+                store_half4(const_cast<__half *>(vbase) + size_t(slot) * kHeadDim + 4 * lane, v);
+            }
+        }
+    }
+    __syncthreads();
+
+    // B fragments of Q^T for the 8 k-steps: b0 = Q[head g][16k + 2t, +1], b1 = Q[head g][16k + 8 + 2t, +1]
+    uint32_t bq[8][2];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        bq[k][0] = *reinterpret_cast<const uint32_t *>(&sm.q[g][16 * k + 2 * t4]);
+        bq[k][1] = *reinterpret_cast<const uint32_t *>(&sm.q[g][16 * k + 8 + 2 * t4]);
+    }
+
+    // Per-thread state for heads 2*t4 and 2*t4+1: running max (replicated over g), partial sum (this thread's keys),
+    // and O^T fragments o[dm] = dims 16*dm + {g, g+8} x heads {2*t4, 2*t4+1}.
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float o[8][4];
+#pragma unroll
+    for (int dm = 0; dm < 8; dm++) o[dm][0] = o[dm][1] = o[dm][2] = o[dm][3] = 0.f;
+
+    const int new_tile = it.fold ? (it.pos - j0) / kTileKeys : -1;
+    const int new_row = it.fold ? (it.pos - j0) % kTileKeys : -1;
+
+    for (int t = 0; t < n_tiles; t++) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        if (t + kStages - 1 < n_tiles) load_tile(t + kStages - 1);
+        cp_async_commit();
+
+        const int stage = t % kStages;
+        const int jw = j0 + t * kTileKeys + 16 * warp;  // first key of this warp's 16-row slice
+        if (jw >= j_end) continue;                       // warp-uniform
+
+        if (t == new_tile && (new_row >> 4) == warp) {
+            // the new token's row comes from registers/shared memory, never from the cache slot being written
+            const uint4 val = lane < 16 ? reinterpret_cast<const uint4 *>(sm.knew)[lane]
+                                        : reinterpret_cast<const uint4 *>(sm.vnew)[lane - 16];
+            unsigned char *tile = lane < 16 ? sm.k[stage] : sm.v[stage];
+            const int ch = lane & 15;
+            *reinterpret_cast<uint4 *>(tile + new_row * kRowBytes + ((ch ^ (new_row & 7)) << 4)) = val;
+            __syncwarp();
+        }
+
+        // S^T (16 keys x 8 heads) = K . Q^T
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint32_t base = ks_addr + stage * kTileBytes + (16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8) * kRowBytes;
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                uint32_t a[4];
+                ldmatrix_x4(a, base + (((2 * k + (lane >> 4)) ^ (lane & 7)) << 4));
+                mma_16816(s, a, bq[k][0], bq[k][1]);
+            }
+        }
+        if (jw + g >= j_end) s[0] = s[1] = -INFINITY;
+        if (jw + g + 8 >= j_end) s[2] = s[3] = -INFINITY;
+
+        float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);
+#pragma unroll
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
+        }
+        // at least one key of the slice is valid, so the new maxima are finite
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float c0 = fast_exp2(m0 - mn0), c1 = fast_exp2(m1 - mn1);
+        const float p0 = fast_exp2(s[0] - mn0), p1 = fast_exp2(s[1] - mn1);
+        const float p2 = fast_exp2(s[2] - mn0), p3 = fast_exp2(s[3] - mn1);
+        l0 = l0 * c0 + (p0 + p2);
+        l1 = l1 * c1 + (p1 + p3);
+        m0 = mn0;
+        m1 = mn1;
+        // P^T as the B operand: b0 = P[key 2t, 2t+1][head g], b1 = keys +8
+        const uint32_t b0 = movmatrix_trans(pack_half2(p0, p1));
+        const uint32_t b1 = movmatrix_trans(pack_half2(p2, p3));
+
+        // O^T (128 dims x 8 heads) = O^T * corr + V^T . P^T
+        {
+            const uint32_t base = vs_addr + stage * kTileBytes + (16 * warp + (lane & 7) + (lane >> 4) * 8) * kRowBytes;
+#pragma unroll
+            for (int dm = 0; dm < 8; dm++) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, base + (((2 * dm + ((lane >> 3) & 1)) ^ (lane & 7)) << 4));
+                o[dm][0] *= c0; o[dm][1] *= c1; o[dm][2] *= c0; o[dm][3] *= c1;
+                mma_16816(o[dm], a, b0, b1);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with the tiles: the K tiles become the merge buffer
+
+    // ---- merge the four warps --------------------------------------------------------------------------------
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+    float *obuf = reinterpret_cast<float *>(&sm.k[0][0]);  // [warp][head][dim]
+    if (g == 0) {
+        sm.red_m[warp][2 * t4] = m0; sm.red_m[warp][2 * t4 + 1] = m1;
+        sm.red_l[warp][2 * t4] = l0; sm.red_l[warp][2 * t4 + 1] = l1;
+    }
+#pragma unroll
+    for (int dm = 0; dm < 8; dm++) {
+        float *ow = obuf + size_t(warp) * kGqa * kHeadDim;
+        ow[(2 * t4) * kHeadDim + 16 * dm + g] = o[dm][0];
+        ow[(2 * t4 + 1) * kHeadDim + 16 * dm + g] = o[dm][1];
+        ow[(2 * t4) * kHeadDim + 16 * dm + g + 8] = o[dm][2];
+        ow[(2 * t4 + 1) * kHeadDim + 16 * dm + g + 8] = o[dm][3];
+    }
+    __syncthreads();
+
+    const int d = tid;  // this thread owns one of the 128 output dims for all 8 heads
+    const bool direct = it.n_split == 1;
+    float *rec_base = direct ? nullptr : p.scratch + (size_t(it.part0) + it.split) * kGqa * kPartialDim;
+#pragma unroll 1
+    for (int h = 0; h < kGqa; h++) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, sm.red_m[w][h]);
+        float L = 0.f, A = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; w++) {
+            const float lw = sm.red_l[w][h];
+            if (lw == 0.f) continue;  // a warp that saw no key: m = -inf, skip (fused.metal:314)
+            const float c = fast_exp2(sm.red_m[w][h] - M);
+            L += lw * c;
+            A += obuf[(size_t(w) * kGqa + h) * kHeadDim + d] * c;
+        }
+        const int head = it.kvh * kGqa + h;
+        if (direct && p.mode == 0) {
+            // single split: fold the sink here (fused.metal:319-322), all in base 2
+            const float sink2 = p.sinks[head] * kLog2e;
+            const float Mf = fmaxf(M, sink2), cs = fast_exp2(M - Mf);
+            store_out(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + d,
+                      A * cs / (L * cs + fast_exp2(sink2 - Mf)));
+        } else {
+            // partial record {acc[128], m, l}, m in natural-log units (fused.metal:324-327)
+            float *rec = direct ? p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim
+                                : rec_base + size_t(h) * kPartialDim;
+            rec[d] = A;
+            if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
+        }
+    }
+    if (direct) return;
+
+    // ---- split-K: the last CTA of the group to arrive merges all of its records (fused.metal:332-350) -------------
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) sm.is_last = (atomicAdd(&p.tickets[it.group], 1) == it.n_split - 1);
+    __syncthreads();
+    if (!sm.is_last) return;
+    __threadfence();
+    const float *grp = p.scratch + size_t(it.part0) * kGqa * kPartialDim;
+#pragma unroll 1
+    for (int h = 0; h < kGqa; h++) {
+        const int head = it.kvh * kGqa + h;
+        const float sink = p.sinks[head];
+        float M = p.mode == 0 ? sink : -INFINITY;
+        for (int s = 0; s < it.n_split; s++) M = fmaxf(M, __ldcg(grp + (size_t(s) * kGqa + h) * kPartialDim + kHeadDim));
+        float L = p.mode == 0 ? __expf(sink - M) : 0.f;
+        float A = 0.f;
+        for (int s = 0; s < it.n_split; s++) {
+            const float *rec = grp + (size_t(s) * kGqa + h) * kPartialDim;
+            const float ls = __ldcg(rec + kHeadDim + 1);
+            if (ls == 0.f) continue;
+            const float c = __expf(__ldcg(rec + kHeadDim) - M);
+            L += ls * c;
+            A += __ldcg(rec + d) * c;
+        }
+        if (p.mode == 0) {
+            store_out(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + d, A / L);
+        } else {
+            float *rec = p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim;
+            rec[d] = A;
+            if (d == 0) { rec[kHeadDim] = M; rec[kHeadDim + 1] = L; }
+        }
+    }
+    if (tid == 0) p.tickets[it.group] = 0;  // ready for the next launch
+}
+
+// Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.
+__global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams p) {
+    const int tok = blockIdx.x / kNHead, head = blockIdx.x % kNHead, d = threadIdx.x;
+    const float sink = p.sinks[head];
+    float M = sink;
+    for (int s = 0; s < p.n_parts; s++)
+        M = fmaxf(M, p.partials[((size_t(s) * p.n + tok) * kNHead + head) * kPartialDim + kHeadDim]);
+    float L = __expf(sink - M), A = 0.f;
+    for (int s = 0; s < p.n_parts; s++) {
+        const float *rec = p.partials + ((size_t(s) * p.n + tok) * kNHead + head) * kPartialDim;
+        const float ls = rec[kHeadDim + 1];
+        if (ls == 0.f) continue;
+        const float c = __expf(rec[kHeadDim] - M);
+        L += ls * c;
+        A += rec[d] * c;
+    }
+    store_out(p.out, p.out_dtype, size_t(tok) * kQDim + head * kHeadDim + d, A / L);
+}
+
+}  // namespace
+
+cudaError_t decode_kernel_setup() {
+    return cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(DecSmem)));
+}
+
+cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) {
+    if (n_items <= 0) return cudaSuccess;
+    k_decode_attn<<<n_items, kThreads, sizeof(DecSmem), stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream) {
+    if (p.n <= 0) return cudaSuccess;
+    k_combine_parts<<<p.n * kNHead, kHeadDim, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace flint

@@ -1,0 +1,598 @@
+// Host side of the attention library: the handle behind include/flint_attn.h, KV-cache ownership, the split-K
+// work planner and the C ABI.  Plays the role of the attention parts of the reference's Engine
+// (src/engine.mm:509-511 cache allocation, :735-766 decode dispatch, :1080-1104 prefill chunk loop) and of its
+// C boundary (src/capi.mm:17-74: try/catch at every entry, message copied into the caller's buffer).
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "../../include/flint_attn.h"
+#include "attn_common.h"
+#include "prefill_attn.h"
+
+using namespace flint;
+
+namespace {
+
+void set_err(char *err, int32_t len, const char *msg) {  // src/capi.mm:17-22
+    if (err && len > 0) {
+        strncpy(err, msg, size_t(len) - 1);
+        err[len - 1] = 0;
+    }
+}
+
+#define CK(call)                                                                                      \
+    do {                                                                                              \
+        cudaError_t e_ = (call);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(e_) + " at " #call); \
+    } while (0)
+
+struct Layer {
+    bool is_swa = false, has_rope = false, has_weights = false;
+    int n_slots = 0;
+    int kv_lo = 0, kv_hi = 0;  // positions a full layer holds on this device: [kv_lo, kv_hi)
+    __half *k = nullptr, *v = nullptr;
+    float *q_norm = nullptr, *k_norm = nullptr, *sinks = nullptr;  // device copies
+};
+
+constexpr int kRing = 4;  // work lists in flight
+
+int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Own split policy.  The reference's (src/engine.mm:742-743: at most 32 splits of at least 256 keys) fills an
+// M5; a B200 wants a few work items per CTA slot on each of its 148 SMs, whatever the batch looks like, so the
+// chunk length is derived from the total number of cached key rows of the whole launch.
+void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi, int target_items,
+                 std::vector<DecItem> &items, int &n_groups, int &n_records) {
+    items.clear();
+    long long total = 0;
+    std::vector<int> lo(n), hi(n);
+    for (int i = 0; i < n; i++) {
+        const int kb = is_swa ? std::max(pos[i] - (kNSwa - 1), 0) : 0;  // src/metal/fused.metal:265
+        lo[i] = std::min(std::max(kb, kv_lo), pos[i]);
+        hi[i] = std::max(lo[i], std::min(pos[i], kv_hi));
+        total += hi[i] - lo[i];
+    }
+    total *= kNHeadKv;
+    if (target_items < 1) target_items = 1;
+    const int chunk = round_up(int(std::max<long long>(256, (total + target_items - 1) / target_items)), 64);
+    n_groups = n * kNHeadKv;
+    n_records = 0;
+    for (int i = 0; i < n; i++) {
+        const int nk = hi[i] - lo[i];
+        const bool own_new = kv_lo <= pos[i] && pos[i] < kv_hi;
+        int n_split = std::max(1, (nk + chunk - 1) / chunk);
+        const int per = std::max(64, round_up((nk + n_split - 1) / n_split, 64));
+        n_split = std::max(1, (nk + per - 1) / per);
+        for (int kvh = 0; kvh < kNHeadKv; kvh++) {
+            const int part0 = n_records;
+            if (n_split > 1) n_records += n_split;
+            for (int s = 0; s < n_split; s++) {
+                DecItem it{};
+                it.tok = i;
+                it.seq = seqs ? seqs[i] : i;
+                it.kvh = kvh;
+                it.pos = pos[i];
+                it.j0 = lo[i] + s * per;
+                it.j1 = std::min(hi[i], lo[i] + (s + 1) * per);
+                it.fold = (own_new && s == n_split - 1) ? 1 : 0;
+                it.split = s;
+                it.n_split = n_split;
+                it.part0 = part0;
+                it.group = i * kNHeadKv + kvh;
+                items.push_back(it);
+            }
+        }
+    }
+    // longest first: the block scheduler hands CTAs out in order, which makes this a greedy LPT schedule
+    std::stable_sort(items.begin(), items.end(),
+                     [](const DecItem &a, const DecItem &b) { return a.j1 - a.j0 > b.j1 - b.j0; });
+}
+
+}  // namespace
+
+struct flint_attn {
+    int device = 0, max_seqs = 0, n_ctx = 0, kv_rank = 0, kv_ranks = 1;
+    int sm_count = 148, target_items = 0;
+    std::vector<Layer> layers;
+    std::vector<int32_t> pos;
+    float *inv_freq = nullptr;
+    float *scratch = nullptr;
+    size_t scratch_recs = 0;
+    int *tickets = nullptr;
+    size_t n_tickets = 0;
+    // pinned host staging for work lists + matching device buffers, reused round-robin behind events
+    DecItem *ring_host[kRing] = {};
+    DecItem *ring_dev[kRing] = {};
+    size_t ring_cap[kRing] = {};
+    cudaEvent_t ring_ev[kRing] = {};
+    int ring_next = 0;
+    cudaStream_t stream = nullptr;  // used by the host-buffer entry points
+    void *io_dev = nullptr;         // device staging for host-buffer calls
+    size_t io_cap = 0;
+    PrefillWorkspace pf;
+    int64_t launches = 0;
+    std::vector<DecItem> items;
+    // optional device timing of the attention kernels alone (events around each launch)
+    bool timing = false;
+    std::vector<cudaEvent_t> ev_pool;
+    size_t ev_used = 0;
+
+    ~flint_attn() {
+        cudaSetDevice(device);
+        for (auto &L : layers) {
+            cudaFree(L.k); cudaFree(L.v); cudaFree(L.q_norm); cudaFree(L.k_norm); cudaFree(L.sinks);
+        }
+        cudaFree(inv_freq); cudaFree(scratch); cudaFree(tickets); cudaFree(io_dev);
+        for (int i = 0; i < kRing; i++) {
+            if (ring_host[i]) cudaFreeHost(ring_host[i]);
+            cudaFree(ring_dev[i]);
+            if (ring_ev[i]) cudaEventDestroy(ring_ev[i]);
+        }
+        prefill_workspace_free(pf);
+        for (cudaEvent_t e : ev_pool) cudaEventDestroy(e);
+        if (stream) cudaStreamDestroy(stream);
+    }
+
+    void time_mark(cudaStream_t st) {
+        if (!timing) return;
+        if (ev_used == ev_pool.size()) {
+            cudaEvent_t e;
+            CK(cudaEventCreate(&e));
+            ev_pool.push_back(e);
+        }
+        CK(cudaEventRecord(ev_pool[ev_used++], st));
+    }
+
+    Layer &layer(int il) {
+        if (il < 0 || il >= int(layers.size())) throw std::runtime_error("layer index out of range");
+        Layer &L = layers[il];
+        if (!L.has_weights) throw std::runtime_error("layer weights not set (flint_attn_set_layer)");
+        return L;
+    }
+
+    void check_seqs(int n, const int32_t *seqs) const {
+        if (n <= 0 || n > max_seqs) throw std::runtime_error("batch size out of range");
+        for (int i = 0; i < n; i++)
+            if (seqs[i] < 0 || seqs[i] >= max_seqs) throw std::runtime_error("sequence index out of range");
+    }
+
+    void ensure_io(size_t bytes) {
+        if (bytes <= io_cap) return;
+        cudaFree(io_dev);
+        io_dev = nullptr;
+        io_cap = 0;
+        CK(cudaMalloc(&io_dev, bytes));
+        io_cap = bytes;
+    }
+
+    // Upload a work list through the pinned ring; returns the device copy, valid for the next launch on `st`.
+    const DecItem *upload_items(cudaStream_t st) {
+        const int r = ring_next;
+        ring_next = (ring_next + 1) % kRing;
+        CK(cudaEventSynchronize(ring_ev[r]));  // the launch that last used this slot has consumed it
+        const size_t need = items.size();
+        if (need > ring_cap[r]) {
+            if (ring_host[r]) cudaFreeHost(ring_host[r]);
+            cudaFree(ring_dev[r]);
+            ring_host[r] = nullptr;
+            ring_dev[r] = nullptr;
+            ring_cap[r] = 0;
+            const size_t cap = std::max<size_t>(need * 2, 1024);
+            CK(cudaMallocHost(&ring_host[r], cap * sizeof(DecItem)));
+            CK(cudaMalloc(&ring_dev[r], cap * sizeof(DecItem)));
+            ring_cap[r] = cap;
+        }
+        memcpy(ring_host[r], items.data(), need * sizeof(DecItem));
+        CK(cudaMemcpyAsync(ring_dev[r], ring_host[r], need * sizeof(DecItem), cudaMemcpyHostToDevice, st));
+        return ring_dev[r];
+    }
+    void mark_ring_used(const DecItem *dev, cudaStream_t st) {
+        for (int i = 0; i < kRing; i++)
+            if (ring_dev[i] == dev) CK(cudaEventRecord(ring_ev[i], st));
+    }
+
+    void ensure_scratch(int n_records, int n_groups) {
+        if (size_t(n_records) > scratch_recs) {
+            CK(cudaDeviceSynchronize());  // earlier launches may still be using the old buffer
+            cudaFree(scratch);
+            scratch = nullptr;
+            scratch_recs = 0;
+            const size_t recs = std::max<size_t>(size_t(n_records) * 2, 4096);
+            CK(cudaMalloc(&scratch, recs * kGqa * kPartialDim * sizeof(float)));
+            scratch_recs = recs;
+        }
+        if (size_t(n_groups) > n_tickets) {
+            CK(cudaDeviceSynchronize());
+            cudaFree(tickets);
+            tickets = nullptr;
+            n_tickets = 0;
+            const size_t nt = std::max<size_t>(size_t(n_groups) * 2, 1024);
+            CK(cudaMalloc(&tickets, nt * sizeof(int)));
+            CK(cudaMemset(tickets, 0, nt * sizeof(int)));
+            n_tickets = nt;
+        }
+    }
+
+    // mode 0: out [n][4096]; mode 1: partial_out [n][32][130]
+    void decode_dev(int il, int n, const int32_t *seqs, const void *qkv, int qkv_dtype, void *out, int out_dtype,
+                    float *partial_out, int mode, cudaStream_t st) {
+        CK(cudaSetDevice(device));
+        Layer &L = layer(il);
+        check_seqs(n, seqs);
+        if (qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) throw std::runtime_error("bad qkv dtype");
+        if (mode == 0 && out_dtype != kDtypeF32 && out_dtype != kDtypeBf16) throw std::runtime_error("bad out dtype");
+        if (mode == 0 && kv_ranks > 1 && !L.is_swa)
+            throw std::runtime_error("full layers of a KV-sharded handle need decode_partial + combine");
+        std::vector<int32_t> p(n);
+        for (int i = 0; i < n; i++) {
+            p[i] = pos[seqs[i]];
+            if (p[i] >= n_ctx) throw std::runtime_error("context full");  // src/engine.mm:904
+            for (int j = 0; j < i; j++)
+                if (seqs[j] == seqs[i]) throw std::runtime_error("a sequence appears twice in one decode batch");
+        }
+        int n_groups = 0, n_records = 0;
+        plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records);
+        ensure_scratch(n_records, n_groups);
+        DecParams dp{};
+        dp.items = upload_items(st);
+        dp.qkv = qkv;
+        dp.out = out;
+        dp.partial_out = partial_out;
+        dp.q_norm = L.q_norm; dp.k_norm = L.k_norm; dp.sinks = L.sinks; dp.inv_freq = inv_freq;
+        dp.k_cache = L.k; dp.v_cache = L.v;
+        dp.scratch = scratch; dp.tickets = tickets;
+        dp.seq_stride = (long long)kNHeadKv * L.n_slots * kHeadDim;
+        dp.n_slots = L.n_slots;
+        dp.slot_mask = L.is_swa ? uint32_t(kSwaRing - 1) : 0xFFFFFFFFu;
+        dp.kv_lo = L.is_swa ? 0 : L.kv_lo;
+        dp.has_rope = L.has_rope;
+        dp.qkv_dtype = qkv_dtype; dp.out_dtype = out_dtype;
+        dp.mode = mode;
+        time_mark(st);
+        CK(launch_decode(dp, int(items.size()), st));
+        time_mark(st);
+        launches++;
+        mark_ring_used(dp.items, st);
+    }
+};
+
+// ============================================================================ C ABI
+#define API_TRY try {
+#define API_CATCH(ret)                       \
+    }                                        \
+    catch (const std::exception &ex) {       \
+        set_err(err, err_len, ex.what());    \
+        return ret;                          \
+    }
+
+extern "C" {
+
+flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err_len) {
+    flint_attn *a = nullptr;
+    try {
+        if (!cfg) throw std::runtime_error("null config");
+        if (cfg->n_layers <= 0 || !cfg->layer_is_swa || !cfg->layer_has_rope) throw std::runtime_error("bad layer table");
+        if (cfg->max_seqs <= 0 || cfg->n_ctx <= 0) throw std::runtime_error("max_seqs and n_ctx must be positive");
+        const int ranks = cfg->kv_ranks > 1 ? cfg->kv_ranks : 1;
+        if (cfg->kv_rank < 0 || cfg->kv_rank >= ranks) throw std::runtime_error("kv_rank out of range");
+        int n_dev = 0;
+        CK(cudaGetDeviceCount(&n_dev));
+        if (cfg->device < 0 || cfg->device >= n_dev) throw std::runtime_error("no such CUDA device");
+        CK(cudaSetDevice(cfg->device));
+        cudaDeviceProp prop{};
+        CK(cudaGetDeviceProperties(&prop, cfg->device));
+        if (prop.major != 10)
+            throw std::runtime_error("this library is built for sm_100a (B200) only; device is sm_" +
+                                     std::to_string(prop.major) + std::to_string(prop.minor));
+        a = new flint_attn();
+        a->device = cfg->device;
+        a->max_seqs = cfg->max_seqs;
+        a->n_ctx = cfg->n_ctx;
+        a->kv_rank = cfg->kv_rank;
+        a->kv_ranks = ranks;
+        a->sm_count = prop.multiProcessorCount;
+        a->target_items = a->sm_count * 2 * 4;
+        a->pos.assign(cfg->max_seqs, 0);
+        CK(cudaStreamCreateWithFlags(&a->stream, cudaStreamNonBlocking));
+        for (int i = 0; i < kRing; i++) CK(cudaEventCreateWithFlags(&a->ring_ev[i], cudaEventDisableTiming));
+        CK(decode_kernel_setup());
+        CK(prefill_kernel_setup());
+        float freq[kHeadDim / 2];
+        for (int i = 0; i < kHeadDim / 2; i++) freq[i] = powf(kRopeTheta, -2.0f * i / kHeadDim);  // ref_model.cpp:55
+        CK(cudaMalloc(&a->inv_freq, sizeof(freq)));
+        CK(cudaMemcpy(a->inv_freq, freq, sizeof(freq), cudaMemcpyHostToDevice));
+        const int shard = (cfg->n_ctx + ranks - 1) / ranks;
+        a->layers.resize(cfg->n_layers);
+        for (int il = 0; il < cfg->n_layers; il++) {
+            Layer &L = a->layers[il];
+            L.is_swa = cfg->layer_is_swa[il] != 0;
+            L.has_rope = cfg->layer_has_rope[il] != 0;
+            if (L.is_swa) {
+                L.n_slots = kSwaRing;  // src/engine.mm:509
+                L.kv_lo = 0;
+                L.kv_hi = INT32_MAX;
+            } else {
+                L.kv_lo = std::min(cfg->n_ctx, a->kv_rank * shard);
+                L.kv_hi = std::min(cfg->n_ctx, L.kv_lo + shard);
+                L.n_slots = std::max(1, L.kv_hi - L.kv_lo);
+            }
+            const size_t bytes = size_t(cfg->max_seqs) * kNHeadKv * L.n_slots * kHeadDim * sizeof(__half);
+            CK(cudaMalloc(&L.k, bytes));
+            CK(cudaMalloc(&L.v, bytes));
+            CK(cudaMemset(L.k, 0, bytes));
+            CK(cudaMemset(L.v, 0, bytes));
+            CK(cudaMalloc(&L.q_norm, kHeadDim * sizeof(float)));
+            CK(cudaMalloc(&L.k_norm, kHeadDim * sizeof(float)));
+            CK(cudaMalloc(&L.sinks, kNHead * sizeof(float)));
+        }
+        CK(cudaDeviceSynchronize());
+        return a;
+    } catch (const std::exception &ex) {
+        set_err(err, err_len, ex.what());
+        delete a;
+        return nullptr;
+    }
+}
+
+void flint_attn_close(flint_attn *a) {
+    if (!a) return;
+    cudaSetDevice(a->device);
+    cudaDeviceSynchronize();
+    delete a;
+}
+
+int32_t flint_attn_n_ctx(const flint_attn *a) { return a->n_ctx; }
+
+int32_t flint_attn_pos(const flint_attn *a, int32_t seq) {
+    if (seq < 0 || seq >= a->max_seqs) return -1;
+    return a->pos[seq];
+}
+
+int32_t flint_attn_truncate(flint_attn *a, int32_t seq, int32_t pos) {  // src/capi.mm:52-56
+    if (seq < 0 || seq >= a->max_seqs) return -1;
+    if (pos < 0 || pos > a->pos[seq]) return -1;
+    a->pos[seq] = pos;
+    return 0;
+}
+
+int32_t flint_attn_rollback_restart(int32_t cached_len, int32_t pos) {  // server/src/main.rs:96-100
+    if (cached_len > pos && cached_len - pos > 511) pos = pos >= 512 ? pos - 512 : 0;
+    return pos;
+}
+
+int32_t flint_attn_set_pos(flint_attn *a, int32_t seq, int32_t pos) {
+    if (seq < 0 || seq >= a->max_seqs || pos < 0 || pos > a->n_ctx) return -1;
+    a->pos[seq] = pos;
+    return 0;
+}
+
+int32_t flint_attn_advance(flint_attn *a, int32_t n, const int32_t *seqs, int32_t n_tokens) {
+    if (n < 0 || n_tokens < 0) return -1;
+    for (int i = 0; i < n; i++)
+        if (seqs[i] < 0 || seqs[i] >= a->max_seqs || a->pos[seqs[i]] + n_tokens > a->n_ctx) return -1;
+    for (int i = 0; i < n; i++) a->pos[seqs[i]] += n_tokens;
+    return 0;
+}
+
+int32_t flint_attn_set_layer(flint_attn *a, int32_t layer, const float *q_norm, const float *k_norm,
+                             const float *sinks, char *err, int32_t err_len) {
+    API_TRY
+    if (layer < 0 || layer >= int(a->layers.size())) throw std::runtime_error("layer index out of range");
+    if (!q_norm || !k_norm || !sinks) throw std::runtime_error("null weight pointer");
+    CK(cudaSetDevice(a->device));
+    Layer &L = a->layers[layer];
+    CK(cudaMemcpy(L.q_norm, q_norm, kHeadDim * sizeof(float), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(L.k_norm, k_norm, kHeadDim * sizeof(float), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(L.sinks, sinks, kNHead * sizeof(float), cudaMemcpyHostToDevice));
+    L.has_weights = true;
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_decode_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs, const void *qkv_dev,
+                              int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
+                              int32_t err_len) {
+    API_TRY
+    a->decode_dev(layer, n, seqs, qkv_dev, qkv_dtype, out_dev, out_dtype, nullptr, 0, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_decode_partial_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs,
+                                      const void *qkv_dev, int32_t qkv_dtype, float *partial_dev, void *cuda_stream,
+                                      char *err, int32_t err_len) {
+    API_TRY
+    a->decode_dev(layer, n, seqs, qkv_dev, qkv_dtype, nullptr, 0, partial_dev, 1, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_combine_dev(flint_attn *a, int32_t layer, int32_t n, int32_t n_parts, const float *partials_dev,
+                               void *out_dev, int32_t out_dtype, void *cuda_stream, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    Layer &L = a->layer(layer);
+    if (n <= 0 || n_parts <= 0) throw std::runtime_error("bad combine shape");
+    if (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16) throw std::runtime_error("bad out dtype");
+    CombineParams cp{partials_dev, L.sinks, out_dev, n, n_parts, out_dtype};
+    CK(launch_combine(cp, cudaStream_t(cuda_stream)));
+    a->launches++;
+    return 0;
+    API_CATCH(-1)
+}
+
+static size_t elem_size(int dtype) { return dtype == kDtypeF32 ? 4 : 2; }
+
+int32_t flint_attn_decode(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs, const void *qkv,
+                          int32_t qkv_dtype, void *out, int32_t out_dtype, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    if (n <= 0 || n > a->max_seqs) throw std::runtime_error("batch size out of range");
+    if ((qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) || (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16))
+        throw std::runtime_error("bad dtype");
+    const size_t in_bytes = size_t(n) * kQkvDim * elem_size(qkv_dtype);
+    const size_t in_pad = (in_bytes + 255) / 256 * 256;
+    const size_t out_bytes = size_t(n) * kQDim * elem_size(out_dtype);
+    a->ensure_io(in_pad + out_bytes);
+    char *d_in = static_cast<char *>(a->io_dev), *d_out = d_in + in_pad;
+    CK(cudaMemcpyAsync(d_in, qkv, in_bytes, cudaMemcpyHostToDevice, a->stream));
+    a->decode_dev(layer, n, seqs, d_in, qkv_dtype, d_out, out_dtype, nullptr, 0, a->stream);
+    CK(cudaMemcpyAsync(out, d_out, out_bytes, cudaMemcpyDeviceToHost, a->stream));
+    CK(cudaStreamSynchronize(a->stream));  // synchronous like the reference (src/engine.mm:930)
+    return 0;
+    API_CATCH(-1)
+}
+
+static void prefill_impl(flint_attn *a, int layer, int seq, int n_tok, const void *qkv, int qkv_dtype, void *out,
+                         int out_dtype, cudaStream_t st) {
+    CK(cudaSetDevice(a->device));
+    Layer &L = a->layer(layer);
+    if (seq < 0 || seq >= a->max_seqs) throw std::runtime_error("sequence index out of range");
+    if (n_tok <= 0) throw std::runtime_error("empty prefill");  // src/engine.mm:975
+    const int p0 = a->pos[seq];
+    if (p0 + n_tok > a->n_ctx) throw std::runtime_error("context full");  // src/engine.mm:976
+    if (a->kv_ranks > 1 && !L.is_swa) throw std::runtime_error("prefill of a KV-sharded full layer is not supported");
+    if ((qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) || (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16))
+        throw std::runtime_error("bad dtype");
+    PrefillParams pp{};
+    pp.qkv = qkv; pp.out = out;
+    pp.qkv_dtype = qkv_dtype; pp.out_dtype = out_dtype;
+    pp.q_norm = L.q_norm; pp.k_norm = L.k_norm; pp.sinks = L.sinks; pp.inv_freq = a->inv_freq;
+    pp.k_cache = L.k + size_t(seq) * kNHeadKv * L.n_slots * kHeadDim;
+    pp.v_cache = L.v + size_t(seq) * kNHeadKv * L.n_slots * kHeadDim;
+    pp.n_slots = L.n_slots;
+    pp.is_swa = L.is_swa; pp.has_rope = L.has_rope;
+    pp.p0 = p0; pp.n_tok = n_tok;
+    int n_launch = 0;
+    a->time_mark(st);
+    CK(launch_prefill(pp, a->pf, st, &n_launch));
+    a->time_mark(st);
+    a->launches += n_launch;
+}
+
+int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv_dev,
+                               int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
+                               int32_t err_len) {
+    API_TRY
+    prefill_impl(a, layer, seq, n_tok, qkv_dev, qkv_dtype, out_dev, out_dtype, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_prefill(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv,
+                           int32_t qkv_dtype, void *out, int32_t out_dtype, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    if (n_tok <= 0) throw std::runtime_error("empty prefill");
+    if ((qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) || (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16))
+        throw std::runtime_error("bad dtype");
+    const size_t in_bytes = size_t(n_tok) * kQkvDim * elem_size(qkv_dtype);
+    const size_t in_pad = (in_bytes + 255) / 256 * 256;
+    const size_t out_bytes = size_t(n_tok) * kQDim * elem_size(out_dtype);
+    a->ensure_io(in_pad + out_bytes);
+    char *d_in = static_cast<char *>(a->io_dev), *d_out = d_in + in_pad;
+    CK(cudaMemcpyAsync(d_in, qkv, in_bytes, cudaMemcpyHostToDevice, a->stream));
+    prefill_impl(a, layer, seq, n_tok, d_in, qkv_dtype, d_out, out_dtype, a->stream);
+    CK(cudaMemcpyAsync(out, d_out, out_bytes, cudaMemcpyDeviceToHost, a->stream));
+    CK(cudaStreamSynchronize(a->stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_n_slots(const flint_attn *a, int32_t layer) {
+    if (layer < 0 || layer >= int(a->layers.size())) return -1;
+    return a->layers[layer].n_slots;
+}
+
+static void kv_copy(flint_attn *a, int layer, int seq, int slot0, int n, uint16_t *k, uint16_t *v, bool to_host) {
+    CK(cudaSetDevice(a->device));
+    if (layer < 0 || layer >= int(a->layers.size())) throw std::runtime_error("layer index out of range");
+    Layer &L = a->layers[layer];
+    if (seq < 0 || seq >= a->max_seqs) throw std::runtime_error("sequence index out of range");
+    if (slot0 < 0 || n < 0 || slot0 + n > L.n_slots) throw std::runtime_error("slot range out of bounds");
+    CK(cudaDeviceSynchronize());
+    for (int kvh = 0; kvh < kNHeadKv; kvh++) {
+        const size_t doff = ((size_t(seq) * kNHeadKv + kvh) * L.n_slots + slot0) * kHeadDim;
+        const size_t hoff = size_t(kvh) * n * kHeadDim, bytes = size_t(n) * kHeadDim * 2;
+        if (to_host) {
+            CK(cudaMemcpy(k + hoff, L.k + doff, bytes, cudaMemcpyDeviceToHost));
+            CK(cudaMemcpy(v + hoff, L.v + doff, bytes, cudaMemcpyDeviceToHost));
+        } else {
+            CK(cudaMemcpy(L.k + doff, k + hoff, bytes, cudaMemcpyHostToDevice));
+            CK(cudaMemcpy(L.v + doff, v + hoff, bytes, cudaMemcpyHostToDevice));
+        }
+    }
+}
+
+int32_t flint_attn_read_kv(flint_attn *a, int32_t layer, int32_t seq, int32_t slot0, int32_t n, uint16_t *k,
+                           uint16_t *v, char *err, int32_t err_len) {
+    API_TRY
+    kv_copy(a, layer, seq, slot0, n, k, v, true);
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_write_kv(flint_attn *a, int32_t layer, int32_t seq, int32_t slot0, int32_t n, const uint16_t *k,
+                            const uint16_t *v, char *err, int32_t err_len) {
+    API_TRY
+    kv_copy(a, layer, seq, slot0, n, const_cast<uint16_t *>(k), const_cast<uint16_t *>(v), false);
+    return 0;
+    API_CATCH(-1)
+}
+
+void *flint_attn_kv_dev(flint_attn *a, int32_t layer, int32_t which) {
+    if (layer < 0 || layer >= int(a->layers.size())) return nullptr;
+    return which == 0 ? static_cast<void *>(a->layers[layer].k) : static_cast<void *>(a->layers[layer].v);
+}
+
+int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, int32_t kv_lo, int32_t kv_hi,
+                               int32_t target_items, int32_t *out, int32_t cap) {
+    std::vector<DecItem> items;
+    int n_groups = 0, n_records = 0;
+    plan_decode(n, nullptr, pos, is_swa != 0, kv_lo, kv_hi, target_items, items, n_groups, n_records);
+    if (int(items.size()) > cap) return -1;
+    for (size_t i = 0; i < items.size(); i++) {
+        const DecItem &it = items[i];
+        const int32_t rec[8] = {it.tok, it.kvh, it.j0, it.j1, it.fold, it.split, it.n_split, it.part0};
+        memcpy(out + 8 * i, rec, sizeof(rec));
+    }
+    return int32_t(items.size());
+}
+
+int32_t flint_attn_set_target_items(flint_attn *a, int32_t target_items) {
+    if (target_items < 1) return -1;
+    a->target_items = target_items;
+    return 0;
+}
+
+int64_t flint_attn_launch_count(const flint_attn *a) { return a->launches; }
+
+int32_t flint_attn_set_timing(flint_attn *a, int32_t on) {
+    a->timing = on != 0;
+    a->ev_used = 0;
+    return 0;
+}
+
+double flint_attn_kernel_ms(flint_attn *a, int64_t *n_timed) {
+    double total = 0;
+    int64_t n = 0;
+    cudaSetDevice(a->device);
+    for (size_t i = 0; i + 1 < a->ev_used; i += 2) {
+        float ms = 0;
+        if (cudaEventSynchronize(a->ev_pool[i + 1]) != cudaSuccess) break;
+        if (cudaEventElapsedTime(&ms, a->ev_pool[i], a->ev_pool[i + 1]) != cudaSuccess) break;
+        total += ms;
+        n++;
+    }
+    a->ev_used = 0;
+    if (n_timed) *n_timed = n;
+    return total;
+}
+
+}  // extern "C"

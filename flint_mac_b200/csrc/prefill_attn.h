@@ -1,0 +1,30 @@
+// Prefill attention launcher (norm/RoPE/cache-write prologue + tcgen05 flash attention).
+#pragma once
+
+#include "attn_common.h"
+
+namespace flint {
+
+struct PrefillParams {
+    const void *qkv;   // [n_tok][5120] fp32 or bf16, raw projections
+    void *out;         // [n_tok][4096] fp32 or bf16
+    const float *q_norm, *k_norm, *sinks, *inv_freq;
+    __half *k_cache, *v_cache;  // this sequence's caches: [4][n_slots][128]
+    int n_slots;
+    int is_swa, has_rope;
+    int p0, n_tok;     // positions p0 .. p0+n_tok-1
+    int qkv_dtype, out_dtype;
+};
+
+// Device scratch that lives with the handle and grows on demand: half-precision staging of the normalised,
+// rotated Q and of the K/V rows a launch attends to.
+struct PrefillWorkspace {
+    void *buf = nullptr;
+    size_t cap = 0;
+};
+
+cudaError_t prefill_kernel_setup();
+cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStream_t stream, int *n_launches);
+void prefill_workspace_free(PrefillWorkspace &ws);
+
+}  // namespace flint

@@ -139,6 +139,12 @@ int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, in
 int32_t flint_attn_set_target_items(flint_attn *a, int32_t target_items);
 /* Number of kernel launches this handle has enqueued so far. */
 int64_t flint_attn_launch_count(const flint_attn *a);
+/* Device timing of the attention launches alone, in the role of the reference's per-dispatch GPU timestamps
+ * (Engine::enable_profiling / last_profile, src/engine.h:49-51): while on, every decode / prefill call is bracketed
+ * by CUDA events on its stream.  flint_attn_kernel_ms waits for them, returns the summed milliseconds and the
+ * number of bracketed calls since the last query, and starts over. */
+int32_t flint_attn_set_timing(flint_attn *a, int32_t on);
+double flint_attn_kernel_ms(flint_attn *a, int64_t *n_timed);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,52 @@
+"""Shared helpers for the parity tests: seeded inputs from the oracle's generator and the tolerances of the task."""
+from __future__ import annotations
+
+import numpy as np
+
+from oracle import oracle as fo
+
+# Attention outputs vs the fp32 reference arithmetic: max-abs 2e-3, mean-abs 2e-4.
+MAX_ABS_TOL = 2e-3
+MEAN_ABS_TOL = 2e-4
+
+KINDS = {  # name -> (is_swa, has_rope)
+    "swa_rope": (True, True),
+    "full_nope": (False, False),
+    "full_rope": (False, True),
+}
+
+
+def assert_close(got: np.ndarray, want: np.ndarray, what: str = ""):
+    got = np.asarray(got, np.float64).reshape(-1)
+    want = np.asarray(want, np.float64).reshape(-1)
+    assert np.isfinite(got).all(), f"{what}: non-finite output"
+    err = np.abs(got - want)
+    assert err.max() <= MAX_ABS_TOL, f"{what}: max-abs {err.max():.3e} > {MAX_ABS_TOL}"
+    assert err.mean() <= MEAN_ABS_TOL, f"{what}: mean-abs {err.mean():.3e} > {MEAN_ABS_TOL}"
+    return float(err.max()), float(err.mean())
+
+
+def synth_cache_f16(seed: int, layer: int, seq: int, n_pos: int):
+    """fp16 K/V ~ N(0,1) for positions [0, n_pos) of one sequence, position-major [n_pos][4][128] half bits."""
+    k = fo.gen_normal(seed, fo.STREAM_KCACHE + 16 * layer + 4096 * seq, n_pos * fo.KV_DIM)
+    v = fo.gen_normal(seed, fo.STREAM_VCACHE + 16 * layer + 4096 * seq, n_pos * fo.KV_DIM)
+    return (fo.to_f16_bits(k).reshape(n_pos, 4, 128), fo.to_f16_bits(v).reshape(n_pos, 4, 128))
+
+
+def to_slot_layout(kv_pos_major: np.ndarray, n_slots: int, is_swa: bool) -> np.ndarray:
+    """[n_pos][4][128] by position -> [4][n_slots][128] by cache slot (ring: the last writer of a slot wins)."""
+    n_pos = kv_pos_major.shape[0]
+    out = np.zeros((4, n_slots, 128), np.uint16)
+    if is_swa:
+        first = max(0, n_pos - n_slots)
+        pos = np.arange(first, n_pos)
+        out[:, pos & (n_slots - 1)] = kv_pos_major[first:].transpose(1, 0, 2)
+    else:
+        out[:, :n_pos] = kv_pos_major.transpose(1, 0, 2)
+    return out
+
+
+def bf16_round_rows(x: np.ndarray):
+    """(rounded fp32 values, uint16 bf16 bits)."""
+    bits = fo.to_bf16_bits(x)
+    return fo.from_bf16_bits(bits), bits
