@@ -60,6 +60,9 @@ SYMBOLS = {
     "flint_attn_launch_count": (C.c_int64, [C.c_void_p]),
     "flint_attn_set_timing": (C.c_int32, [C.c_void_p, C.c_int32]),
     "flint_attn_kernel_ms": (C.c_double, [C.c_void_p, C.POINTER(C.c_int64)]),
+    "flint_attn_decode_noalloc_dev": (C.c_int32, [C.c_int32, C.POINTER(C.c_int32), C.c_void_p, C.c_int32, C.c_void_p,
+                                                  C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
 }
 
 _lib = None
@@ -110,6 +113,18 @@ def plan_decode(pos: Sequence[int], is_swa: bool, kv_lo: int = 0, kv_hi: int = 2
 
 def rollback_restart(cached_len: int, pos: int) -> int:
     return int(load_library().flint_attn_rollback_restart(cached_len, pos))
+
+
+def decode_noalloc_dev(pos: Sequence[int], qkv_dev, qkv_dtype: int, out_dev, out_dtype: int, k_cache_dev, v_cache_dev,
+                       n_slots: int, is_swa: bool, has_rope: bool, q_norm_dev, k_norm_dev, sinks_dev, stream: int = 0):
+    """Handle-free decode attention that allocates nothing (flint_attn_decode_noalloc_dev): every buffer is the
+    caller's, the scratch is a fixed array inside the library.  At most 64 tokens per call."""
+    err = C.create_string_buffer(ERR_LEN)
+    r = load_library().flint_attn_decode_noalloc_dev(
+        len(pos), _i32(pos), _ptr(qkv_dev), qkv_dtype, _ptr(out_dev), out_dtype, _ptr(k_cache_dev), _ptr(v_cache_dev),
+        n_slots, int(is_swa), int(has_rope), _ptr(q_norm_dev), _ptr(k_norm_dev), _ptr(sinks_dev), stream, err, ERR_LEN)
+    if r != 0:
+        raise FlintAttnError(err.value.decode(errors="replace"))
 
 
 class Attn:

@@ -146,6 +146,34 @@ int64_t flint_attn_launch_count(const flint_attn *a);
 int32_t flint_attn_set_timing(flint_attn *a, int32_t on);
 double flint_attn_kernel_ms(flint_attn *a, int64_t *n_timed);
 
+/* ---- decode without any allocation -----------------------------------------------------------------
+ * No counterpart in the reference (whose engine allocates what it needs, src/engine.mm:509-521); added for
+ * hosts that cannot allocate device memory when they need attention: a server whose own arena already owns the
+ * GPU (the KV caches live there), a plug-in inside a framework that owns the allocator, or a latency-critical
+ * section where a device allocation's implicit synchronisation is not acceptable.  The handle-based calls above
+ * allocate (caches at open; scratch and staging on demand); this one calls no cudaMalloc / cudaFree /
+ * cudaMallocHost and uses no handle.  Same kernel and same arithmetic as flint_attn_decode_dev.
+ *
+ * The caller owns and passes everything as device pointers: qkv rows [n][5120], out rows [n][4096], the K and V
+ * caches of the n sequences, half [n][4][n_slots][128] (row i of the batch uses cache i; n_slots = 1024 on a
+ * sliding-window layer, the context length otherwise), q_norm/k_norm [128] and sinks [32] in fp32.  pos is a
+ * HOST array of the n token positions.  What the kernel needs beyond that (work list, split-K partial records,
+ * arrival counters, RoPE table) sits in one fixed array inside the library image, about 8.4 MiB on every GPU that
+ * loads the library, held until the process exits.  Limits: n <= FLINT_ATTN_NOALLOC_MAX_TOKENS and a split-K work
+ * list of at most FLINT_ATTN_NOALLOC_MAX_ITEMS items; beyond either the call fails with a message and does nothing.
+ *
+ * The first call on each device resolves the array's device address, fills the RoPE table and clears the
+ * counters with blocking operations on the default stream: make that first call before any stream capture begins.
+ * All calls on a device share the one array, and it keeps the previous call's partial records: two calls that may
+ * overlap on the GPU (different streams, or different host threads) race on it -- issue them on one stream or
+ * order them yourself.  Host-side it is not re-entrant either. */
+enum { FLINT_ATTN_NOALLOC_MAX_TOKENS = 64, FLINT_ATTN_NOALLOC_MAX_ITEMS = 2048 };
+int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, const void *qkv_dev, int32_t qkv_dtype,
+                                      void *out_dev, int32_t out_dtype, void *k_cache_dev, void *v_cache_dev,
+                                      int32_t n_slots, int32_t is_swa, int32_t has_rope, const float *q_norm_dev,
+                                      const float *k_norm_dev, const float *sinks_dev, void *cuda_stream, char *err,
+                                      int32_t err_len);
+
 #ifdef __cplusplus
 }
 #endif
