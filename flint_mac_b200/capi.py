@@ -47,6 +47,7 @@ SYMBOLS = {
                                        C.c_int32, C.c_char_p, C.c_int32]),
     "flint_attn_prefill_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
                                            C.c_int32, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_check": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32]),
     "flint_attn_n_slots": (C.c_int32, [C.c_void_p, C.c_int32]),
     "flint_attn_read_kv": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
                                        C.c_char_p, C.c_int32]),
@@ -221,6 +222,10 @@ class Attn:
     def prefill_dev(self, layer, seq, n_tok, qkv_dev, qkv_dtype, out_dev, out_dtype, stream: int = 0):
         self._call("flint_attn_prefill_dev", layer, seq, n_tok, _ptr(qkv_dev), qkv_dtype, _ptr(out_dev), out_dtype,
                    stream)
+
+    def check(self):
+        """Synchronise and raise if any asynchronous call of this handle failed on the device."""
+        self._call("flint_attn_check")
 
     # ---- cache access (tests, cache pre-loading)
     def read_kv(self, layer: int, seq: int, slot0: int, n: int):

@@ -501,6 +501,20 @@ int32_t flint_attn_prefill(flint_attn *a, int32_t layer, int32_t seq, int32_t n_
     prefill_impl(a, layer, seq, n_tok, d_in, qkv_dtype, d_out, out_dtype, a->stream);
     CK(cudaMemcpyAsync(out, d_out, out_bytes, cudaMemcpyDeviceToHost, a->stream));
     CK(cudaStreamSynchronize(a->stream));
+    int flag = 0;
+    CK(prefill_error_flag(a->pf, &flag));
+    if (flag) throw std::runtime_error("prefill kernel reported device error " + std::to_string(flag));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_check(flint_attn *a, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    CK(cudaDeviceSynchronize());
+    int flag = 0;
+    CK(prefill_error_flag(a->pf, &flag));
+    if (flag) throw std::runtime_error("prefill kernel reported device error " + std::to_string(flag));
     return 0;
     API_CATCH(-1)
 }

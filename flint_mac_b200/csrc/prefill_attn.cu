@@ -1,7 +1,476 @@
+// Prefill attention for sm_100a: a norm/RoPE/cache-write prologue and a tcgen05 flash-attention kernel.
+//
+// Replaces the reference's k_qk_prefill + k_attn_prefill chunk loop (src/metal/prefill.metal:100-266,
+// src/engine.mm:1080-1104).  Semantics kept: RMSNorm then NEOX RoPE at position p0+t on q and k, K/V stored as half in
+// the cache slot (pos & 1023 on ring layers), causal + 513-key window mask per element, the learned sink as the
+// initial running maximum with l0 = 1 so that it only enters the denominator (prefill.metal:162), P rounded to half
+// before P.V (prefill.metal:223), fp32 scores / statistics / accumulators.
+//
+// Shape chosen for B200: one CTA owns 128 query rows = 16 consecutive positions x the 8 query heads of one KV head,
+// so one K/V tile serves the whole GQA group and the key band of a CTA is 512+16 keys wide instead of 512+128.
+// Q, K and V tiles arrive by TMA (128-byte swizzle, no multicast) from half-precision staging written by the
+// prologue; S = Q.K^T and O += P.V run on the 5th-generation tensor core (tcgen05.mma, kind::f16) with both
+// accumulators in tensor memory; each thread owns one query row of S (tcgen05.ld 32x32b), so the softmax needs no
+// shuffles; O is rescaled lazily (only when a row maximum grows by more than 2^8).
 #include "prefill_attn.h"
 
+#include <cuda.h>
+
+#include "ptx.cuh"
+#include "tc5.cuh"
+
 namespace flint {
-cudaError_t prefill_kernel_setup() { return cudaSuccess; }
-cudaError_t launch_prefill(const PrefillParams &, PrefillWorkspace &, cudaStream_t, int *n) { *n = 0; return cudaErrorNotSupported; }
-void prefill_workspace_free(PrefillWorkspace &ws) { cudaFree(ws.buf); ws.buf = nullptr; ws.cap = 0; }
+
+namespace {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kQPos = 16;             // query positions per CTA
+constexpr int kBM = kQPos * kGqa;     // 128 query rows
+constexpr int kBN = 64;               // keys per tile
+constexpr int kStages = 2;
+constexpr int kTmemCols = 256;        // S: columns [0, 64), O: columns [64, 192)
+constexpr int kColS = 0, kColO = 64;
+constexpr int kHist = kNSwa - 1;      // 512 keys of history a sliding-window query can see
+
+constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB, two 64-dim halves of [128 rows][128 B]
+constexpr int kKBytes = kBN * kHeadDim * 2;   // 16 KiB, two halves of [64 keys][128 B]
+constexpr int kPBytes = kBM * kBN * 2;        // 16 KiB, [128 rows][64 keys]
+constexpr int kOffQ = 0;
+constexpr int kOffK = kOffQ + kQBytes;
+constexpr int kOffV = kOffK + kStages * kKBytes;
+constexpr int kOffP = kOffV + kStages * kKBytes;
+constexpr int kOffBar = kOffP + kPBytes;
+constexpr int kSmemBytes = kOffBar + 64;  // 114752 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
+
+struct PfArgs {
+    void *out;
+    const float *sinks;
+    int *error_flag;
+    int out_dtype;
+    int p0, n_tok, is_swa;
+    int key_row0;  // key position held by row 0 of the K/V tensor maps
+};
+
+// ------------------------------------------------------------------------------------------------- prologue
+struct PrologueArgs {
+    const void *qkv;
+    const float *q_norm, *k_norm, *inv_freq;
+    __half *k_cache, *v_cache;  // [4][n_slots][128] of this sequence
+    __half *q_st;               // [32][n_tok][128], pre-scaled by log2(e)/sqrt(128)
+    __half *k_st, *v_st;        // [4][n_hist + n_tok][128] (ring layers only; null otherwise)
+    int n_slots, is_swa, has_rope, qkv_dtype;
+    int p0, n_tok, n_hist;
+    int history_pass;  // 1: only copy the history rows out of the ring; 0: only the new tokens
+};
+
+__device__ __forceinline__ float4 pf_load_row4(const void *base, int dtype, size_t elem0, int lane) {
+    if (dtype == kDtypeF32) return reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem0)[lane];
+    const uint2 u = reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + elem0)[lane];
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&u.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
+
+__device__ __forceinline__ float4 pf_norm_rope(float4 v, const float *w, const float *inv_freq, int lane, int pos, bool rope) {
+    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
+    const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps);
+    const float4 wv = reinterpret_cast<const float4 *>(w)[lane];
+    float x[4] = {v.x * scale * wv.x, v.y * scale * wv.y, v.z * scale * wv.z, v.w * scale * wv.w};
+    if (rope) {
+        const float4 fr = reinterpret_cast<const float4 *>(inv_freq)[lane & 15];
+        const float freq[4] = {fr.x, fr.y, fr.z, fr.w};
+        float out[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float partner = __shfl_xor_sync(0xffffffffu, x[j], 16);
+            float s, c;
+            sincosf(float(pos) * freq[j], &s, &c);
+            out[j] = lane < 16 ? x[j] * c - partner * s : partner * s + x[j] * c;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) x[j] = out[j];
+    }
+    return make_float4(x[0], x[1], x[2], x[3]);
+}
+
+__device__ __forceinline__ void pf_store_half4(__half *dst, float4 v) {
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
+}
+
+// New-token pass: one warp per (token, head slot): 32 q heads, 4 k heads, 4 v heads.  History pass (ring layers
+// with p0 > 0): one warp per (history row, kv head) copies the up to 512 keys before p0 out of the ring into the
+// linear staging the attention kernel reads.  The history pass is its own, earlier launch: tokens p0+512.. of a
+// long prompt land in the very ring slots the history occupies (which is why the reference prefills in chunks of
+// at most 512, src/metal/flint_config.h:29-31).
+__global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 8 + warp;
+    const long long n_main = a.history_pass ? 0 : (long long)a.n_tok * 40;
+    if (!a.history_pass && row >= n_main) return;
+    if (row < n_main) {
+        const int t = int(row / 40), hs = int(row % 40), pos = a.p0 + t;
+        const size_t in0 = size_t(t) * kQkvDim;
+        if (hs < kNHead) {
+            float4 q = pf_load_row4(a.qkv, a.qkv_dtype, in0 + size_t(hs) * kHeadDim, lane);
+            q = pf_norm_rope(q, a.q_norm, a.inv_freq, lane, pos, a.has_rope != 0);
+            const float sc = rsqrtf(float(kHeadDim)) * kLog2e;
+            q.x *= sc; q.y *= sc; q.z *= sc; q.w *= sc;
+            pf_store_half4(a.q_st + (size_t(hs) * a.n_tok + t) * kHeadDim + 4 * lane, q);
+            return;
+        }
+        const bool is_k = hs < kNHead + kNHeadKv;
+        const int kvh = is_k ? hs - kNHead : hs - kNHead - kNHeadKv;
+        float4 x = pf_load_row4(a.qkv, a.qkv_dtype, in0 + kQDim + (is_k ? 0 : kKvDim) + size_t(kvh) * kHeadDim, lane);
+        if (is_k) x = pf_norm_rope(x, a.k_norm, a.inv_freq, lane, pos, a.has_rope != 0);
+        const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos;  // prefill.metal:106
+        __half *cache = is_k ? a.k_cache : a.v_cache;
+        pf_store_half4(cache + (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane, x);
+        if (a.k_st) {
+            __half *st = is_k ? a.k_st : a.v_st;
+            pf_store_half4(st + (size_t(kvh) * (a.n_hist + a.n_tok) + a.n_hist + t) * kHeadDim + 4 * lane, x);
+        }
+        return;
+    }
+    const long long hrow = row - n_main;  // history copy (ring layers with p0 > 0)
+    if (hrow >= (long long)a.n_hist * kNHeadKv) return;
+    const int r = int(hrow / kNHeadKv), kvh = int(hrow % kNHeadKv);
+    const int pos = a.p0 - a.n_hist + r, slot = pos & (kSwaRing - 1);
+    const size_t src = (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane;
+    const size_t dst = (size_t(kvh) * (a.n_hist + a.n_tok) + r) * kHeadDim + 4 * lane;
+    *reinterpret_cast<uint2 *>(a.k_st + dst) = *reinterpret_cast<const uint2 *>(a.k_cache + src);
+    *reinterpret_cast<uint2 *>(a.v_st + dst) = *reinterpret_cast<const uint2 *>(a.v_cache + src);
+}
+
+// ------------------------------------------------------------------------------------------------- attention
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
+    // bounded in wall-clock time: ~0.25 s, far beyond anything a healthy launch needs
+    if (tc5::mbar_try_wait(bar, parity)) return true;
+    uint64_t t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        if (tc5::mbar_try_wait(bar, parity)) return true;
+        uint64_t t1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        if (t1 - t0 > 250000000ull) return false;
+    }
+}
+
+__global__ void __launch_bounds__(kBM, 2) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
+                                                         const __grid_constant__ CUtensorMap tm_k,
+                                                         const __grid_constant__ CUtensorMap tm_v, const PfArgs a) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    unsigned char *gen = smem_raw;
+    if (base & 1023u) {  // swizzled tiles need 1024-byte alignment; nothing has been allocated yet
+        if (threadIdx.x == 0) atomicExch(a.error_flag, 2);
+        return;
+    }
+    const uint32_t sQ = base + kOffQ, sK = base + kOffK, sV = base + kOffV, sP = base + kOffP;
+    const uint32_t bar_q = base + kOffBar, bar_full0 = bar_q + 8, bar_mma = bar_q + 24;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 32);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int kvh = blockIdx.y;
+    const int t0 = blockIdx.x * kQPos;
+    const int hl = tid >> 4, qi = tid & 15;  // row = head-in-group * 16 + position-in-block (the TMA box order)
+    const int q_first = a.p0 + t0;
+    const int qpos = q_first + qi;
+    const bool row_valid = t0 + qi < a.n_tok;
+    const int q_last = a.p0 + min(t0 + kQPos, a.n_tok) - 1;
+    const int klo = a.is_swa ? max(q_first - kHist, a.key_row0) : 0;
+    const int n_tiles = (q_last - klo) / kBN + 1;
+
+    if (tid == 0) {
+        tc5::mbar_init(bar_q, 1);
+        tc5::mbar_init(bar_full0, 1);
+        tc5::mbar_init(bar_full0 + 8, 1);
+        tc5::mbar_init(bar_mma, 1);
+        tc5::mbar_fence_init();
+    }
+    if (warp == 0) {
+        tc5::tmem_alloc(base + kOffBar + 32, kTmemCols);
+        tc5::tmem_relinquish();
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    tc5::fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    auto load_kv = [&](int kt) {
+        const int st = kt & 1;
+        const uint32_t bar = bar_full0 + 8 * st;
+        const int row = klo + kt * kBN - a.key_row0;
+        tc5::mbar_expect_tx(bar, 2 * kKBytes);
+        tc5::tma_load_3d(sK + st * kKBytes, &tm_k, bar, 0, row, kvh);
+        tc5::tma_load_3d(sK + st * kKBytes + kKBytes / 2, &tm_k, bar, 64, row, kvh);
+        tc5::tma_load_3d(sV + st * kKBytes, &tm_v, bar, 0, row, kvh);
+        tc5::tma_load_3d(sV + st * kKBytes + kKBytes / 2, &tm_v, bar, 64, row, kvh);
+    };
+    if (tid == 0) {
+        tc5::prefetch_tmap(&tm_q);
+        tc5::prefetch_tmap(&tm_k);
+        tc5::prefetch_tmap(&tm_v);
+        tc5::mbar_expect_tx(bar_q, kQBytes);
+        tc5::tma_load_3d(sQ, &tm_q, bar_q, 0, t0, kvh * kGqa);
+        tc5::tma_load_3d(sQ + kQBytes / 2, &tm_q, bar_q, 64, t0, kvh * kGqa);
+        load_kv(0);
+    }
+
+    constexpr uint32_t kIdescQK = tc5::idesc_f16(kBM, kBN, 0, 0);        // A = Q (K-major), B = K (K-major)
+    constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);   // A = P (K-major), B = V (MN-major)
+
+    const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
+    float m = sink2, l = 1.0f;  // prefill.metal:162
+    uint32_t mma_phase = 0;
+    bool ok = __all_sync(0xffffffffu, wait_bar(bar_q, 0));  // kept warp-uniform: tcgen05.ld/st are warp-wide
+    const uint32_t lane_base = tmem + (uint32_t(warp * 32) << 16);
+
+    for (int kt = 0; kt < n_tiles && ok; kt++) {
+        const int st = kt & 1;
+        // the other stage was last read by the P.V product of tile kt-1, which every thread has waited for
+        if (tid == 0 && kt + 1 < n_tiles) load_kv(kt + 1);
+        ok = __all_sync(0xffffffffu, wait_bar(bar_full0 + 8 * st, (kt >> 1) & 1));
+        if (!ok) break;
+        if (tid == 0) {
+            tc5::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < kHeadDim / 16; ks++) {
+                const uint32_t koff = (ks >> 2) * (kQBytes / 2) + (ks & 3) * 32;
+                const uint32_t kboff = (ks >> 2) * (kKBytes / 2) + (ks & 3) * 32;
+                tc5::mma_f16_ss(tmem + kColS, tc5::smem_desc_sw128(sQ + koff, 16, 1024),
+                                tc5::smem_desc_sw128(sK + st * kKBytes + kboff, 16, 1024), kIdescQK, ks > 0);
+            }
+            tc5::mma_commit(bar_mma);
+        }
+        ok = __all_sync(0xffffffffu, wait_bar(bar_mma, mma_phase));
+        mma_phase ^= 1;
+        if (!ok) break;
+        tc5::fence_after_sync();
+
+        // ---- this thread's row of S: mask, running max, probabilities
+        float s[kBN];
+        {
+            uint32_t r0[32], r1[32];
+            tc5::tmem_ld32(lane_base + kColS, r0);
+            tc5::tmem_ld32(lane_base + kColS + 32, r1);
+            tc5::tmem_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 32; c++) {
+                s[c] = __uint_as_float(r0[c]);
+                s[c + 32] = __uint_as_float(r1[c]);
+            }
+        }
+        const int kbase = klo + kt * kBN;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < kBN; c++) {
+            const int kpos = kbase + c;
+            const bool vis = row_valid && kpos <= qpos && (!a.is_swa || qpos - kpos <= kHist);  // prefill.metal:212
+            s[c] = vis ? s[c] : -INFINITY;
+            mx = fmaxf(mx, s[c]);
+        }
+        // lazy rescale: keep the old reference maximum unless the row maximum outgrew it by more than 2^8
+        float corr = 1.0f;
+        if (kt == 0) {
+            m = fmaxf(m, mx);
+            l = fast_exp2(sink2 - m);  // the sink's share of the denominator under the new maximum
+        } else if (mx > m + 8.0f) {
+            corr = fast_exp2(m - mx);
+            m = mx;
+            l *= corr;
+        }
+        if (kt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+            for (int cb = 0; cb < kHeadDim; cb += 32) {
+                uint32_t r[32];
+                tc5::tmem_ld32(lane_base + kColO + cb, r);
+                tc5::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                tc5::tmem_st32(lane_base + kColO + cb, r);
+            }
+            tc5::tmem_wait_st();
+        }
+        {
+            float sum = 0.f;
+            unsigned char *prow = gen + kOffP + tid * (kBN * 2);
+#pragma unroll
+            for (int ch = 0; ch < kBN / 8; ch++) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float p0 = fast_exp2(s[ch * 8 + 2 * j] - m), p1 = fast_exp2(s[ch * 8 + 2 * j + 1] - m);
+                    sum += p0 + p1;
+                    w[j] = pack_half2(p0, p1);
+                }
+                *reinterpret_cast<uint4 *>(prow + ((ch ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l += sum;
+        }
+        tc5::fence_proxy_async();
+        tc5::fence_before_sync();
+        __syncthreads();
+        if (tid == 0) {
+            tc5::fence_after_sync();
+#pragma unroll
+            for (int ks = 0; ks < kBN / 16; ks++) {
+                tc5::mma_f16_ss(tmem + kColO, tc5::smem_desc_sw128(sP + ks * 32, 16, 1024),
+                                tc5::smem_desc_sw128(sV + st * kKBytes + ks * 2048, kKBytes / 2, 1024), kIdescPV,
+                                (kt > 0 || ks > 0));
+            }
+            tc5::mma_commit(bar_mma);
+        }
+        ok = __all_sync(0xffffffffu, wait_bar(bar_mma, mma_phase));
+        mma_phase ^= 1;
+        if (!ok) break;
+        tc5::fence_after_sync();
+    }
+
+    if (ok) {
+        const float inv_l = 1.0f / l;  // prefill.metal:255-265
+        const size_t o0 = (size_t(t0 + qi) * kNHead + kvh * kGqa + hl) * kHeadDim;
+#pragma unroll
+        for (int cb = 0; cb < kHeadDim; cb += 32) {
+            uint32_t r[32];
+            tc5::tmem_ld32(lane_base + kColO + cb, r);
+            tc5::tmem_wait_ld();
+            if (row_valid) {
+                if (a.out_dtype == kDtypeF32) {
+                    float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(a.out) + o0 + cb);
+#pragma unroll
+                    for (int c = 0; c < 8; c++)
+                        dst[c] = make_float4(__uint_as_float(r[4 * c]) * inv_l, __uint_as_float(r[4 * c + 1]) * inv_l,
+                                             __uint_as_float(r[4 * c + 2]) * inv_l, __uint_as_float(r[4 * c + 3]) * inv_l);
+                } else {
+                    uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(a.out) + o0 + cb);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]) * inv_l,
+                                                                           __uint_as_float(r[8 * c + 2 * j + 1]) * inv_l);
+                            w[j] = *reinterpret_cast<const uint32_t *>(&b);
+                        }
+                        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    } else if (tid == 0) {
+        atomicExch(a.error_flag, 1);  // a wait ran out: report, then leave through the normal teardown
+    }
+    tc5::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tc5::tmem_dealloc(tmem, kTmemCols);
+}
+
+// ------------------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// half tensor [n_outer][n_rows][128] viewed as 3-D {128, n_rows, n_outer}, box {64, box_rows, box_outer}
+cudaError_t make_map(CUtensorMap *map, const void *base, int n_rows, int n_outer, int box_rows, int box_outer) {
+    const cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(n_rows), cuuint64_t(n_outer)};
+    const cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * 2, cuuint64_t(n_rows) * kHeadDim * 2};
+    const cuuint32_t box[3] = {64, cuuint32_t(box_rows), cuuint32_t(box_outer)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box,
+                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t prefill_kernel_setup() {
+    if (!g_encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (!fn || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    return cudaFuncSetAttribute(k_prefill_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+}
+
+void prefill_workspace_free(PrefillWorkspace &ws) {
+    cudaFree(ws.buf);
+    ws.buf = nullptr;
+    ws.cap = 0;
+}
+
+cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStream_t stream, int *n_launches) {
+    *n_launches = 0;
+    const int T = p.n_tok;
+    const int n_hist = p.is_swa ? (p.p0 < kHist ? p.p0 : kHist) : 0;
+    auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+    const size_t q_bytes = up(size_t(kNHead) * T * kHeadDim * 2);
+    const size_t kv_bytes = p.is_swa ? up(size_t(kNHeadKv) * (n_hist + T) * kHeadDim * 2) : 0;
+    const size_t need = q_bytes + 2 * kv_bytes + 1024;
+    if (need > ws.cap) {
+        cudaError_t e = cudaDeviceSynchronize();  // an earlier launch may still be reading the old staging
+        if (e != cudaSuccess) return e;
+        cudaFree(ws.buf);
+        ws.buf = nullptr;
+        ws.cap = 0;
+        e = cudaMalloc(&ws.buf, need);
+        if (e != cudaSuccess) return e;
+        ws.cap = need;
+        e = cudaMemset(ws.buf, 0, 1024);
+        if (e != cudaSuccess) return e;
+    }
+    char *wbase = static_cast<char *>(ws.buf);
+    int *err_flag = reinterpret_cast<int *>(wbase);
+    __half *q_st = reinterpret_cast<__half *>(wbase + 1024);
+    __half *k_st = p.is_swa ? reinterpret_cast<__half *>(wbase + 1024 + q_bytes) : nullptr;
+    __half *v_st = p.is_swa ? reinterpret_cast<__half *>(wbase + 1024 + q_bytes + kv_bytes) : nullptr;
+
+    PrologueArgs pa{};
+    pa.qkv = p.qkv; pa.q_norm = p.q_norm; pa.k_norm = p.k_norm; pa.inv_freq = p.inv_freq;
+    pa.k_cache = p.k_cache; pa.v_cache = p.v_cache;
+    pa.q_st = q_st; pa.k_st = k_st; pa.v_st = v_st;
+    pa.n_slots = p.n_slots; pa.is_swa = p.is_swa; pa.has_rope = p.has_rope; pa.qkv_dtype = p.qkv_dtype;
+    pa.p0 = p.p0; pa.n_tok = T; pa.n_hist = n_hist;
+    cudaError_t e;
+    if (n_hist > 0) {
+        pa.history_pass = 1;
+        k_prefill_prologue<<<unsigned((n_hist * kNHeadKv + 7) / 8), 256, 0, stream>>>(pa);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        (*n_launches)++;
+    }
+    pa.history_pass = 0;
+    k_prefill_prologue<<<unsigned(((long long)T * 40 + 7) / 8), 256, 0, stream>>>(pa);
+    if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    (*n_launches)++;
+
+    CUtensorMap tm_q, tm_k, tm_v;
+    if ((e = make_map(&tm_q, q_st, T, kNHead, kQPos, kGqa)) != cudaSuccess) return e;
+    const void *kb = p.is_swa ? static_cast<const void *>(k_st) : static_cast<const void *>(p.k_cache);
+    const void *vb = p.is_swa ? static_cast<const void *>(v_st) : static_cast<const void *>(p.v_cache);
+    const int kv_rows = p.is_swa ? n_hist + T : p.n_slots;
+    if ((e = make_map(&tm_k, kb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
+    if ((e = make_map(&tm_v, vb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
+
+    PfArgs a{};
+    a.out = p.out; a.sinks = p.sinks; a.error_flag = err_flag; a.out_dtype = p.out_dtype;
+    a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
+    a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
+    const dim3 grid((T + kQPos - 1) / kQPos, kNHeadKv);
+    k_prefill_attn<<<grid, kBM, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    (*n_launches)++;
+    return cudaSuccess;
+}
+
+cudaError_t prefill_error_flag(const PrefillWorkspace &ws, int *flag) {
+    *flag = 0;
+    if (!ws.buf) return cudaSuccess;
+    return cudaMemcpy(flag, ws.buf, sizeof(int), cudaMemcpyDeviceToHost);
+}
+
+}  // namespace flint

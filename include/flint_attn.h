@@ -113,6 +113,11 @@ int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_
                                int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
                                int32_t err_len);
 
+/* Wait for everything this handle enqueued and report an asynchronous failure of the *_dev calls (a CUDA error,
+ * or a kernel whose bounded wait ran out), in the way the reference turns cb.error into an exception after
+ * waitUntilCompleted (src/engine.mm:930-932). */
+int32_t flint_attn_check(flint_attn *a, char *err, int32_t err_len);
+
 /* ---- cache access for tests and cache pre-loading (counterpart of the Engine::debug_* hooks, src/engine.h:37-47)
  * Cache layout on the device, per layer: K and V separately, half [max_seqs][4][n_slots][128], n_slots = 1024
  * (SWA) or the shard's share of n_ctx (full).  k/v host arrays here: [4][n][128] half bits for slots

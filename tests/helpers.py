@@ -50,3 +50,25 @@ def bf16_round_rows(x: np.ndarray):
     """(rounded fp32 values, uint16 bf16 bits)."""
     bits = fo.to_bf16_bits(x)
     return fo.from_bf16_bits(bits), bits
+
+
+def oracle_at_positions(qkv: np.ndarray, weights, is_swa: bool, has_rope: bool, positions, round_kv_f16=False,
+                        p0: int = 0):
+    """Reference attention (src/ref arithmetic) at selected positions only: norm/RoPE every token to build the K/V
+    history, then attend for the chosen ones.  qkv rows are positions p0.. ; returns ([len(positions)][4096], kc, vc)."""
+    qn, kn, sinks = weights
+    T = qkv.shape[0]
+    rows = np.stack([fo.qk_norm_rope(qkv[t], qn, kn, p0 + t, has_rope) for t in range(T)])
+    kc = np.zeros((p0 + T, fo.KV_DIM), np.float32)
+    vc = np.zeros((p0 + T, fo.KV_DIM), np.float32)
+    kc[p0:] = rows[:, fo.Q_DIM:fo.Q_DIM + fo.KV_DIM]
+    vc[p0:] = rows[:, fo.Q_DIM + fo.KV_DIM:]
+    if round_kv_f16:
+        kc, vc = fo.round_f16(kc), fo.round_f16(vc)
+    out = np.empty((len(positions), fo.Q_DIM), np.float32)
+    for i, p in enumerate(positions):
+        att = np.empty(fo.Q_DIM, np.float32)
+        fo.lib().fo_attend(np.ascontiguousarray(rows[p - p0, :fo.Q_DIM]), kc.reshape(-1), vc.reshape(-1), sinks, p,
+                           int(is_swa), att, 8)
+        out[i] = att
+    return out, kc, vc

@@ -1,0 +1,168 @@
+"""Prefill attention on the GPU (norm/RoPE/cache-write prologue + tcgen05 flash attention), through the C ABI,
+against the CPU oracle and the reference's golden vectors."""
+import os
+
+import numpy as np
+import pytest
+
+from helpers import KINDS, assert_close, bf16_round_rows, oracle_at_positions
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+PROBES = [0, 1, 31, 32, 200, 511, 512, 513, 600, 1023, 1024, 1100, 1299]  # src/main.mm:280
+
+
+@pytest.fixture(scope="module")
+def fa():
+    import flint_mac_b200 as fa
+
+    fa.load_library()
+    return fa
+
+
+def _open(fa, kind, n_ctx, max_seqs=1):
+    return fa.Attn([KINDS[kind][0]], [KINDS[kind][1]], max_seqs, n_ctx)
+
+
+def _prefill_chunks(fa, h, qkv, chunk, dtype=None):
+    T = qkv.shape[0]
+    out = np.empty((T, 4096), np.float32)
+    for c0 in range(0, T, chunk):
+        n = min(chunk, T - c0)
+        o = np.empty((n, 4096), np.float32)
+        h.prefill(0, 0, n, np.ascontiguousarray(qkv[c0:c0 + n]), fa.F32, o, fa.F32)
+        h.advance([0], n)
+        out[c0:c0 + n] = o
+    return out
+
+
+@pytest.mark.parametrize("kind", list(KINDS))
+@pytest.mark.parametrize("T", [1, 15, 16, 17, 40, 130])
+def test_small_prompts_every_position(fa, fo, kind, T):
+    is_swa, has_rope = KINDS[kind]
+    w = fo.layer_weights(4, 0)
+    qkv = fo.raw_qkv(4, 0, 0, T)
+    want, _, _ = fo.layer_forward(qkv, *w, is_swa, has_rope)
+    with _open(fa, kind, 256) as h:
+        h.set_layer(0, *w)
+        got = _prefill_chunks(fa, h, qkv, T)
+    assert_close(got, want, f"{kind} T={T}")
+
+
+@pytest.mark.parametrize("kind", ["full_nope", "swa_rope", "full_rope"])
+@pytest.mark.parametrize("chunk", [512, 1300])
+def test_attn_1300_tokens_like_the_reference_test(fa, fo, kind, chunk):
+    """The reference's test-attn (src/main.mm:240-314): 1300 tokens in chunks of 512 (512/512/276), a full/NoPE and a
+    SWA/RoPE layer, probes at query-block, window and ring-wrap edges -- and the same prompt in a single launch."""
+    is_swa, has_rope = KINDS[kind]
+    seed, T = 0, 1300
+    w = fo.layer_weights(seed, 2)
+    qkv = fo.raw_qkv(seed, 2, 0, T)
+    with _open(fa, kind, 2048) as h:
+        h.set_layer(0, *w)
+        got = _prefill_chunks(fa, h, qkv, chunk)
+        want, kc, vc = fo.layer_forward(qkv, *w, is_swa, has_rope, n_threads=8)
+        assert_close(got, want, f"{kind} chunk={chunk} all positions")
+        assert_close(got[PROBES], want[PROBES], f"{kind} chunk={chunk} probes")
+        # the reference's own pass bar: max_err / rms < 2e-2 (src/main.mm:308)
+        rms = np.sqrt((want[PROBES].astype(np.float64) ** 2).mean())
+        assert np.abs(got[PROBES] - want[PROBES]).max() / rms < 2e-2
+        # cache / ring contents after the prompt: V bit-exact in the slot its position owns
+        n_slots = h.n_slots(0)
+        k_dev, v_dev = h.read_kv(0, 0, 0, n_slots)
+        owners = fo.ring_owners(T) if is_swa else np.arange(T)
+        for s in range(len(owners)):
+            p = int(owners[s])
+            if p < 0:
+                continue
+            assert np.array_equal(v_dev[:, s].reshape(-1), fo.to_f16_bits(vc[p])), (s, p)
+            assert np.abs(fo.from_f16_bits(k_dev[:, s].reshape(-1)) - kc[p]).max() <= np.abs(kc[p]).max() * 2 ** -9
+
+
+@pytest.mark.parametrize("kind", list(KINDS))
+def test_golden_vectors_of_the_reference(fa, fo, kind):
+    g = np.load(os.path.join(GOLD, f"ref_attn_{kind}.npz"))
+    seed, layer, T = int(g["seed"]), int(g["layer"]), int(g["n_tok"])
+    x = np.zeros((T, 9216), np.float32)
+    x[:, :5120] = fo.raw_qkv(seed, layer, 0, T)
+    ones = np.ones(9216, np.float32)
+    qkv = np.stack([fo.rmsnorm(x[t], ones)[:5120] for t in range(T)])
+    with _open(fa, kind, 1300) as h:
+        h.set_layer(0, *fo.layer_weights(seed, layer))
+        got = _prefill_chunks(fa, h, qkv, 512).reshape(T, 32, 128)
+    assert_close(got[g["probe_pos"]], g["probe_att"], f"{kind} golden probes")
+    assert np.abs(got.reshape(T, -1).astype(np.float64).sum(1) - g["row_sum"]).max() < 4096 * 2e-4
+
+
+def test_config3_4000_token_prompt_swa_bf16(fa, fo):
+    """One 4000-token prompt on a SWA layer, bf16 q/k/v, window 512 + sink, K/V into the 1024-slot ring; output
+    checked on the last 256 positions, ring contents on all 1024 slots."""
+    seed, T = 3, 4000
+    w = fo.layer_weights(seed, 0)
+    qkv, bits = bf16_round_rows(fo.raw_qkv(seed, 0, 0, T))
+    with _open(fa, "swa_rope", 4096) as h:
+        h.set_layer(0, *w)
+        out = np.empty((T, 4096), np.float32)
+        h.prefill(0, 0, T, bits, fa.BF16, out, fa.F32)
+        assert np.isfinite(out).all()
+        last = list(range(T - 256, T))
+        want, kc, vc = oracle_at_positions(qkv, w, True, True, last)
+        assert_close(out[last], want, "config 3, last 256 positions")
+        k_dev, v_dev = h.read_kv(0, 0, 0, 1024)
+        owners = fo.ring_owners(T)
+        assert owners.min() == T - 1024
+        for s in range(1024):
+            p = int(owners[s])
+            assert np.array_equal(v_dev[:, s].reshape(-1), fo.to_f16_bits(vc[p])), (s, p)
+        # a few earlier positions too (window edges of the first blocks)
+        some = [0, 15, 16, 511, 512, 513, 1023, 1024, 2047, 2048]
+        want2, _, _ = oracle_at_positions(qkv, w, True, True, some)
+        assert_close(out[some], want2, "config 3, early positions")
+
+
+@pytest.mark.parametrize("kind", ["swa_rope", "full_rope"])
+def test_prefill_then_decode_equals_decode_only(fa, fo, kind):
+    """The reference's check-prefill idea (src/main.mm:317-346) at the kernel level: prefill the first part, decode the
+    rest token by token; both paths must agree with the oracle, and so with each other."""
+    is_swa, has_rope = KINDS[kind]
+    seed, T, split = 6, 1200, 700
+    w = fo.layer_weights(seed, 0)
+    qkv = fo.raw_qkv(seed, 0, 0, T)
+    want, _, _ = fo.layer_forward(qkv, *w, is_swa, has_rope, n_threads=8)
+    with _open(fa, kind, 2048) as h:
+        h.set_layer(0, *w)
+        got = np.empty((T, 4096), np.float32)
+        got[:split] = _prefill_chunks(fa, h, qkv[:split], 512)
+        assert h.pos(0) == split
+        row = np.empty(4096, np.float32)
+        for t in range(split, T):
+            h.decode(0, [0], np.ascontiguousarray(qkv[t]), fa.F32, row, fa.F32)
+            h.advance([0])
+            got[t] = row
+        # then prefill again on top of decoded history (window crosses prefill- and decode-written ring slots)
+        extra = fo.raw_qkv(seed, 0, T, 100)
+        o2 = np.empty((100, 4096), np.float32)
+        h.prefill(0, 0, 100, extra, fa.F32, o2, fa.F32)
+    assert_close(got, want, f"{kind} prefill+decode")
+    want2, _, _ = fo.layer_forward(np.concatenate([qkv, extra]), *w, is_swa, has_rope, n_threads=8)
+    assert_close(o2, want2[T:], f"{kind} prefill on decoded history")
+
+
+def test_rollback_and_recompute(fa, fo):
+    """truncate + the server's rule (server/src/main.rs:96-100): rolling back up to 511 tokens needs nothing; more
+    needs a re-prefill from p-512, after which outputs from p on are those of an uninterrupted run."""
+    seed, T = 8, 1900
+    w = fo.layer_weights(seed, 0)
+    qkv = fo.raw_qkv(seed, 0, 0, T)
+    want, _, _ = fo.layer_forward(qkv, *w, True, True, n_threads=8)
+    for back in (300, 511, 512, 600):
+        with _open(fa, "swa_rope", 2048) as h:
+            h.set_layer(0, *w)
+            _prefill_chunks(fa, h, qkv, 512)
+            p = T - back
+            restart = fa.rollback_restart(T, p)
+            assert restart == (p if back <= 511 else p - 512)
+            assert h.truncate(0, restart) == 0 and h.pos(0) == restart
+            redo = np.empty((T - restart, 4096), np.float32)
+            h.prefill(0, 0, T - restart, np.ascontiguousarray(qkv[restart:]), fa.F32, redo, fa.F32)
+            assert_close(redo[p - restart:], want[p:], f"rollback by {back}")
