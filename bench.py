@@ -202,6 +202,59 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
+def measure_prefill(torch, fa, fo, local, iters: int, warmup: int):
+    """Prefill workload: one 4000-token prompt on a sliding-window layer (window 512 + sink, causal), bf16 q/k/v rows,
+    positions 0..3999, K/V into the 1024-slot ring.  L2 is flushed between iterations.  Returns a dict."""
+    _, tensor_peak, peak_kind = measured_peaks()
+    T = PREFILL_T
+    h = fa.Attn([True], [True], 1, T + 96, device=local)
+    h.set_layer(0, *fo.layer_weights(0, 0))
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    qkv = torch.randn(T, QKV_DIM, generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.empty(T, OUT_DIM, device="cuda", dtype=torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    step_ms = []
+    h.set_timing(True)
+    for i in range(warmup + iters):
+        h.set_pos(0, 0)
+        flush.fill_(i & 0xFF)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if i == warmup:
+            torch.cuda.synchronize()
+            h.kernel_ms()  # drop the warm-up records
+        e0.record()
+        h.prefill_dev(0, 0, T, qkv, fa.BF16, out, fa.BF16, stream)
+        e1.record()
+        if i >= warmup:
+            step_ms.append((e0, e1))
+    torch.cuda.synchronize()
+    attn_ms, n = h.kernel_ms()
+    h.set_timing(False)
+    h.check()
+    attn_us = attn_ms / max(n, 1) * 1e3
+    step_us = float(np.median([a.elapsed_time(b) for a, b in step_ms])) * 1e3
+    flops = prefill_flops(T)
+    tflops = flops / (attn_us * 1e-6) / 1e12
+    # end to end through the host-buffer entry point
+    qkv_host, out_host = qkv.cpu().pin_memory(), torch.empty(T, OUT_DIM, dtype=torch.bfloat16).pin_memory()
+    e2e = []
+    for i in range(3 + min(iters, 10)):
+        h.set_pos(0, 0)
+        t0 = time.perf_counter()
+        h.prefill(0, 0, T, qkv_host, fa.BF16, out_host, fa.BF16)
+        e2e.append(time.perf_counter() - t0)
+    e2e_us = float(np.median(e2e[3:])) * 1e6
+    h.close()
+    return {"workload": "prefill: one 4000-token prompt, SWA layer (window 512 + sink, causal), bf16 rows, ring write",
+            "algorithmic_flops": flops, "attn_kernel_us": attn_us, "tflops": tflops, "peak_tflops": tensor_peak,
+            "frac": tflops / tensor_peak, "peak_kind": f"of {peak_kind} (burst)", "step_us": step_us,
+            "tok_per_s": T / (step_us * 1e-6), "iters": n, "l2": "flushed between iterations (256 MiB write)",
+            "e2e_us": e2e_us, "e2e_tok_per_s": T / (e2e_us * 1e-6), "e2e_tflops": flops / (e2e_us * 1e-6) / 1e12,
+            "h2d_bytes_per_step": T * QKV_DIM * 2, "d2h_bytes_per_step": T * OUT_DIM * 2,
+            "gpu_launches_per_step": 2, "checksum": float(out_host.float().abs().mean())}
+
+
 def run_decode(args):
     import torch
 
@@ -240,12 +293,13 @@ def run_decode(args):
     h.set_timing(True)
     launches0 = h.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clk:
-        ev0.record()
-        for i in range(args.steps):
-            step(args.warmup + i)
-        ev1.record()
-        barrier(world)
+    clk = ClockSampler(local)
+    clk.__enter__()
+    ev0.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    ev1.record()
+    barrier(world)
     ms_total = max_over_ranks(ev0.elapsed_time(ev1), world)
     kernel_ms, n_timed = h.kernel_ms()
     h.set_timing(False)
@@ -270,8 +324,16 @@ def run_decode(args):
         h.advance(seqs, 1)
     barrier(world)
     e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3, world) / args.steps
+    clk.__exit__()
     e2e_value = step_bytes * world / (e2e_ms * 1e-3) / 1e9
     checksum = float(out_host.float().abs().mean())
+    h.close()
+    prefill = None
+    if world == 1 or rank == 0:
+        with ClockSampler(local) as clk_pf:
+            prefill = measure_prefill(torch, fa, fo, local, iters=30, warmup=5)
+        prefill["clocks"] = clk_pf.summary()
+    barrier(world)
 
     line = None
     if rank == 0:
@@ -300,16 +362,16 @@ def run_decode(args):
                              "sample": "4 of 64 sequences x 2 repeats of the same step, OpenMP over heads",
                              "tok_per_s": 1.0 / sec_per_seq, "wall_s": time.perf_counter() - t_cpu0},
             "clocks": clk.summary(),
+            "prefill": prefill,
         }
-    h.close()
     return line, rank, world
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode"])
     args = ap.parse_args()

@@ -28,8 +28,9 @@ constexpr int kQPos = 16;             // query positions per CTA
 constexpr int kBM = kQPos * kGqa;     // 128 query rows
 constexpr int kBN = 64;               // keys per tile
 constexpr int kStages = 2;
-constexpr int kTmemCols = 256;        // S: columns [0, 64), O: columns [64, 192)
-constexpr int kColS = 0, kColO = 64;
+constexpr int kTmemCols = 256;        // S (double-buffered): columns [0, 128), O: columns [128, 256)
+constexpr int kColS = 0, kColO = 128;
+constexpr int kThreadsAttn = kBM + 32; // 4 softmax warps + 1 issuing warp
 constexpr int kHist = kNSwa - 1;      // 512 keys of history a sliding-window query can see
 
 constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB, two 64-dim halves of [128 rows][128 B]
@@ -40,7 +41,7 @@ constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKBytes;
 constexpr int kOffP = kOffV + kStages * kKBytes;
 constexpr int kOffBar = kOffP + kPBytes;
-constexpr int kSmemBytes = kOffBar + 64;  // 114752 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
+constexpr int kSmemBytes = kOffBar + 128;  // 114816 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
 
 struct PfArgs {
     void *out;
@@ -71,21 +72,19 @@ __device__ __forceinline__ float4 pf_load_row4(const void *base, int dtype, size
     return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
 
-__device__ __forceinline__ float4 pf_norm_rope(float4 v, const float *w, const float *inv_freq, int lane, int pos, bool rope) {
+// RMSNorm with weight, then NEOX RoPE with this token's (cos, sin) per owned dim; lane owns dims 4*lane..4*lane+3 and
+// pairs with lane^16 (same arithmetic as src/ref/ref_model.cpp:45-61).
+__device__ __forceinline__ float4 pf_norm_rope(float4 v, const float4 wv, const float (&cs)[4], const float (&sn)[4],
+                                               int lane, bool rope) {
     const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
     const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps);
-    const float4 wv = reinterpret_cast<const float4 *>(w)[lane];
     float x[4] = {v.x * scale * wv.x, v.y * scale * wv.y, v.z * scale * wv.z, v.w * scale * wv.w};
     if (rope) {
-        const float4 fr = reinterpret_cast<const float4 *>(inv_freq)[lane & 15];
-        const float freq[4] = {fr.x, fr.y, fr.z, fr.w};
         float out[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const float partner = __shfl_xor_sync(0xffffffffu, x[j], 16);
-            float s, c;
-            sincosf(float(pos) * freq[j], &s, &c);
-            out[j] = lane < 16 ? x[j] * c - partner * s : partner * s + x[j] * c;
+            out[j] = lane < 16 ? x[j] * cs[j] - partner * sn[j] : partner * sn[j] + x[j] * cs[j];
         }
 #pragma unroll
         for (int j = 0; j < 4; j++) x[j] = out[j];
@@ -97,48 +96,63 @@ __device__ __forceinline__ void pf_store_half4(__half *dst, float4 v) {
     *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
 }
 
-// New-token pass: one warp per (token, head slot): 32 q heads, 4 k heads, 4 v heads.  History pass (ring layers
-// with p0 > 0): one warp per (history row, kv head) copies the up to 512 keys before p0 out of the ring into the
-// linear staging the attention kernel reads.  The history pass is its own, earlier launch: tokens p0+512.. of a
-// long prompt land in the very ring slots the history occupies (which is why the reference prefills in chunks of
-// at most 512, src/metal/flint_config.h:29-31).
+// New-token pass: one warp per (token, group of 8 head rows): groups 0-3 are the 32 q heads, group 4 the 4 k and
+// 4 v heads.  The 8 rows are loaded up front (8 independent loads per lane) and the token's cos/sin are computed
+// once per warp, not once per head.  History pass (ring layers with p0 > 0): one warp per (history row, kv head)
+// copies the up to 512 keys before p0 out of the ring into the linear staging the attention kernel reads.  The
+// history pass is its own, earlier launch: tokens p0+512.. of a long prompt land in the very ring slots the history
+// occupies (which is why the reference prefills in chunks of at most 512, src/metal/flint_config.h:29-31).
 __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long row = (long long)blockIdx.x * 8 + warp;
-    const long long n_main = a.history_pass ? 0 : (long long)a.n_tok * 40;
-    if (!a.history_pass && row >= n_main) return;
-    if (row < n_main) {
-        const int t = int(row / 40), hs = int(row % 40), pos = a.p0 + t;
-        const size_t in0 = size_t(t) * kQkvDim;
-        if (hs < kNHead) {
-            float4 q = pf_load_row4(a.qkv, a.qkv_dtype, in0 + size_t(hs) * kHeadDim, lane);
-            q = pf_norm_rope(q, a.q_norm, a.inv_freq, lane, pos, a.has_rope != 0);
-            const float sc = rsqrtf(float(kHeadDim)) * kLog2e;
+    if (a.history_pass) {
+        if (row >= (long long)a.n_hist * kNHeadKv) return;
+        const int r = int(row / kNHeadKv), kvh = int(row % kNHeadKv);
+        const int pos = a.p0 - a.n_hist + r, slot = pos & (kSwaRing - 1);
+        const size_t src = (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane;
+        const size_t dst = (size_t(kvh) * (a.n_hist + a.n_tok) + r) * kHeadDim + 4 * lane;
+        *reinterpret_cast<uint2 *>(a.k_st + dst) = *reinterpret_cast<const uint2 *>(a.k_cache + src);
+        *reinterpret_cast<uint2 *>(a.v_st + dst) = *reinterpret_cast<const uint2 *>(a.v_cache + src);
+        return;
+    }
+    if (row >= (long long)a.n_tok * 5) return;
+    const int t = int(row / 5), grp = int(row % 5), pos = a.p0 + t;
+    const size_t in0 = size_t(t) * kQkvDim + size_t(grp) * 8 * kHeadDim;  // group 4 starts at 4096: k heads then v heads
+    float4 x[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] = pf_load_row4(a.qkv, a.qkv_dtype, in0 + size_t(i) * kHeadDim, lane);
+    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (a.has_rope) {
+        const float4 fr = reinterpret_cast<const float4 *>(a.inv_freq)[lane & 15];
+        const float freq[4] = {fr.x, fr.y, fr.z, fr.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) sincosf(float(pos) * freq[j], &sn[j], &cs[j]);
+    }
+    if (grp < 4) {
+        const float4 wv = reinterpret_cast<const float4 *>(a.q_norm)[lane];
+        const float sc = rsqrtf(float(kHeadDim)) * kLog2e;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float4 q = pf_norm_rope(x[i], wv, cs, sn, lane, a.has_rope != 0);
             q.x *= sc; q.y *= sc; q.z *= sc; q.w *= sc;
-            pf_store_half4(a.q_st + (size_t(hs) * a.n_tok + t) * kHeadDim + 4 * lane, q);
-            return;
-        }
-        const bool is_k = hs < kNHead + kNHeadKv;
-        const int kvh = is_k ? hs - kNHead : hs - kNHead - kNHeadKv;
-        float4 x = pf_load_row4(a.qkv, a.qkv_dtype, in0 + kQDim + (is_k ? 0 : kKvDim) + size_t(kvh) * kHeadDim, lane);
-        if (is_k) x = pf_norm_rope(x, a.k_norm, a.inv_freq, lane, pos, a.has_rope != 0);
-        const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos;  // prefill.metal:106
-        __half *cache = is_k ? a.k_cache : a.v_cache;
-        pf_store_half4(cache + (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane, x);
-        if (a.k_st) {
-            __half *st = is_k ? a.k_st : a.v_st;
-            pf_store_half4(st + (size_t(kvh) * (a.n_hist + a.n_tok) + a.n_hist + t) * kHeadDim + 4 * lane, x);
+            pf_store_half4(a.q_st + (size_t(grp * 8 + i) * a.n_tok + t) * kHeadDim + 4 * lane, q);
         }
         return;
     }
-    const long long hrow = row - n_main;  // history copy (ring layers with p0 > 0)
-    if (hrow >= (long long)a.n_hist * kNHeadKv) return;
-    const int r = int(hrow / kNHeadKv), kvh = int(hrow % kNHeadKv);
-    const int pos = a.p0 - a.n_hist + r, slot = pos & (kSwaRing - 1);
-    const size_t src = (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane;
-    const size_t dst = (size_t(kvh) * (a.n_hist + a.n_tok) + r) * kHeadDim + 4 * lane;
-    *reinterpret_cast<uint2 *>(a.k_st + dst) = *reinterpret_cast<const uint2 *>(a.k_cache + src);
-    *reinterpret_cast<uint2 *>(a.v_st + dst) = *reinterpret_cast<const uint2 *>(a.v_cache + src);
+    const float4 wk = reinterpret_cast<const float4 *>(a.k_norm)[lane];
+    const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos;  // prefill.metal:106
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const bool is_k = i < kNHeadKv;
+        const int kvh = i & (kNHeadKv - 1);
+        const float4 y = is_k ? pf_norm_rope(x[i], wk, cs, sn, lane, a.has_rope != 0) : x[i];
+        __half *cache = is_k ? a.k_cache : a.v_cache;
+        pf_store_half4(cache + (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane, y);
+        if (a.k_st) {
+            __half *st = is_k ? a.k_st : a.v_st;
+            pf_store_half4(st + (size_t(kvh) * (a.n_hist + a.n_tok) + a.n_hist + t) * kHeadDim + 4 * lane, y);
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------- attention
@@ -155,9 +169,17 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
     }
 }
 
-__global__ void __launch_bounds__(kBM, 2) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
-                                                         const __grid_constant__ CUtensorMap tm_k,
-                                                         const __grid_constant__ CUtensorMap tm_v, const PfArgs a) {
+// Barriers (8 bytes each, at kOffBar): the issuing thread and the 128 softmax threads only ever talk through these.
+enum { kBarQ = 0, kBarKFull = 1, kBarVFull = 3, kBarSReady = 5, kBarPReady = 7, kBarPvDone = 8, kNumBars = 9 };
+
+// 160 threads: warps 0-3 own the 128 query rows (softmax, P, lazy rescale, epilogue); lane 0 of warp 4 issues every
+// TMA copy and every MMA.  Tile kt's S = Q.K^T is issued before the softmax of tile kt-1 has finished (S is double
+// buffered in tensor memory), so the tensor core works on the next scores while the CUDA cores exponentiate the
+// current ones; two such CTAs share an SM.
+__global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
+                                                                  const __grid_constant__ CUtensorMap tm_k,
+                                                                  const __grid_constant__ CUtensorMap tm_v,
+                                                                  const PfArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     unsigned char *gen = smem_raw;
@@ -166,199 +188,229 @@ __global__ void __launch_bounds__(kBM, 2) k_prefill_attn(const __grid_constant__
         return;
     }
     const uint32_t sQ = base + kOffQ, sK = base + kOffK, sV = base + kOffV, sP = base + kOffP;
-    const uint32_t bar_q = base + kOffBar, bar_full0 = bar_q + 8, bar_mma = bar_q + 24;
-    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 32);
+    auto bar = [&](int i) { return base + kOffBar + 8u * uint32_t(i); };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int kvh = blockIdx.y;
     const int t0 = blockIdx.x * kQPos;
-    const int hl = tid >> 4, qi = tid & 15;  // row = head-in-group * 16 + position-in-block (the TMA box order)
     const int q_first = a.p0 + t0;
-    const int qpos = q_first + qi;
-    const bool row_valid = t0 + qi < a.n_tok;
     const int q_last = a.p0 + min(t0 + kQPos, a.n_tok) - 1;
     const int klo = a.is_swa ? max(q_first - kHist, a.key_row0) : 0;
     const int n_tiles = (q_last - klo) / kBN + 1;
 
     if (tid == 0) {
-        tc5::mbar_init(bar_q, 1);
-        tc5::mbar_init(bar_full0, 1);
-        tc5::mbar_init(bar_full0 + 8, 1);
-        tc5::mbar_init(bar_mma, 1);
+        for (int i = 0; i < kNumBars; i++) tc5::mbar_init(bar(i), i == kBarPReady ? kBM : 1);
         tc5::mbar_fence_init();
     }
     if (warp == 0) {
-        tc5::tmem_alloc(base + kOffBar + 32, kTmemCols);
+        tc5::tmem_alloc(base + kOffBar + 8 * kNumBars, kTmemCols);
         tc5::tmem_relinquish();
     }
     tc5::fence_before_sync();
     __syncthreads();
     tc5::fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    bool ok = true;
 
-    auto load_kv = [&](int kt) {
-        const int st = kt & 1;
-        const uint32_t bar = bar_full0 + 8 * st;
-        const int row = klo + kt * kBN - a.key_row0;
-        tc5::mbar_expect_tx(bar, 2 * kKBytes);
-        tc5::tma_load_3d(sK + st * kKBytes, &tm_k, bar, 0, row, kvh);
-        tc5::tma_load_3d(sK + st * kKBytes + kKBytes / 2, &tm_k, bar, 64, row, kvh);
-        tc5::tma_load_3d(sV + st * kKBytes, &tm_v, bar, 0, row, kvh);
-        tc5::tma_load_3d(sV + st * kKBytes + kKBytes / 2, &tm_v, bar, 64, row, kvh);
-    };
-    if (tid == 0) {
-        tc5::prefetch_tmap(&tm_q);
-        tc5::prefetch_tmap(&tm_k);
-        tc5::prefetch_tmap(&tm_v);
-        tc5::mbar_expect_tx(bar_q, kQBytes);
-        tc5::tma_load_3d(sQ, &tm_q, bar_q, 0, t0, kvh * kGqa);
-        tc5::tma_load_3d(sQ + kQBytes / 2, &tm_q, bar_q, 64, t0, kvh * kGqa);
-        load_kv(0);
-    }
+    if (warp == 4) {
+        // =========================================================== issuer: TMA + tcgen05.mma, one thread
+        if ((tid & 31) == 0) {
+            constexpr uint32_t kIdescQK = tc5::idesc_f16(kBM, kBN, 0, 0);       // A = Q (K-major), B = K (K-major)
+            constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);  // A = P (K-major), B = V (MN-major)
+            auto load_k = [&](int kt) {
+                const int st = kt & 1, row = klo + kt * kBN - a.key_row0;
+                tc5::mbar_expect_tx(bar(kBarKFull + st), kKBytes);
+                tc5::tma_load_3d(sK + st * kKBytes, &tm_k, bar(kBarKFull + st), 0, row, kvh);
+                tc5::tma_load_3d(sK + st * kKBytes + kKBytes / 2, &tm_k, bar(kBarKFull + st), 64, row, kvh);
+            };
+            auto load_v = [&](int kt) {
+                const int st = kt & 1, row = klo + kt * kBN - a.key_row0;
+                tc5::mbar_expect_tx(bar(kBarVFull + st), kKBytes);
+                tc5::tma_load_3d(sV + st * kKBytes, &tm_v, bar(kBarVFull + st), 0, row, kvh);
+                tc5::tma_load_3d(sV + st * kKBytes + kKBytes / 2, &tm_v, bar(kBarVFull + st), 64, row, kvh);
+            };
+            auto issue_qk = [&](int kt) {
+                const int st = kt & 1;
+#pragma unroll
+                for (int ks = 0; ks < kHeadDim / 16; ks++) {
+                    const uint32_t qoff = (ks >> 2) * (kQBytes / 2) + (ks & 3) * 32;
+                    const uint32_t koff = (ks >> 2) * (kKBytes / 2) + (ks & 3) * 32;
+                    tc5::mma_f16_ss(tmem + kColS + st * kBN, tc5::smem_desc_sw128(sQ + qoff, 16, 1024),
+                                    tc5::smem_desc_sw128(sK + st * kKBytes + koff, 16, 1024), kIdescQK, ks > 0);
+                }
+                tc5::mma_commit(bar(kBarSReady + st));
+            };
+            tc5::prefetch_tmap(&tm_q);
+            tc5::prefetch_tmap(&tm_k);
+            tc5::prefetch_tmap(&tm_v);
+            tc5::mbar_expect_tx(bar(kBarQ), kQBytes);
+            tc5::tma_load_3d(sQ, &tm_q, bar(kBarQ), 0, t0, kvh * kGqa);
+            tc5::tma_load_3d(sQ + kQBytes / 2, &tm_q, bar(kBarQ), 64, t0, kvh * kGqa);
+            load_k(0);
+            if (n_tiles > 1) load_k(1);
+            load_v(0);
+            if (n_tiles > 1) load_v(1);
+            ok = wait_bar(bar(kBarQ), 0) && wait_bar(bar(kBarKFull), 0);
+            if (ok) issue_qk(0);
+            for (int kt = 0; kt < n_tiles && ok; kt++) {
+                const int st = kt & 1;
+                if (kt + 1 < n_tiles) {
+                    // S[(kt+1)&1] was drained by the softmax of tile kt-1 (its P-ready arrival was waited for below)
+                    ok = wait_bar(bar(kBarKFull + (st ^ 1)), ((kt + 1) >> 1) & 1);
+                    if (!ok) break;
+                    issue_qk(kt + 1);
+                }
+                if (kt >= 1 && kt + 1 < n_tiles) {
+                    // V stage of tile kt-1 is free once its P.V product has completed
+                    ok = wait_bar(bar(kBarPvDone), (kt - 1) & 1);
+                    if (!ok) break;
+                    load_v(kt + 1);
+                }
+                if (kt + 2 < n_tiles) {
+                    // K stage of tile kt is free once Q.K^T of tile kt has completed
+                    ok = wait_bar(bar(kBarSReady + st), (kt >> 1) & 1);
+                    if (!ok) break;
+                    load_k(kt + 2);
+                }
+                ok = wait_bar(bar(kBarPReady), kt & 1) && wait_bar(bar(kBarVFull + st), (kt >> 1) & 1);
+                if (!ok) break;
+                tc5::fence_after_sync();
+#pragma unroll
+                for (int ks = 0; ks < kBN / 16; ks++)
+                    tc5::mma_f16_ss(tmem + kColO, tc5::smem_desc_sw128(sP + ks * 32, 16, 1024),
+                                    tc5::smem_desc_sw128(sV + st * kKBytes + ks * 2048, kKBytes / 2, 1024), kIdescPV,
+                                    (kt > 0 || ks > 0));
+                tc5::mma_commit(bar(kBarPvDone));
+            }
+            if (!ok) atomicExch(a.error_flag, 1);
+        }
+    } else {
+        // =========================================================== softmax warps: one query row per thread
+        const int hl = tid >> 4, qi = tid & 15;  // row = head-in-group * 16 + position-in-block (the TMA box order)
+        const int qpos = q_first + qi;
+        const bool row_valid = t0 + qi < a.n_tok;
+        const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
+        float m = sink2, l = 1.0f;  // prefill.metal:162
+        const uint32_t lane_base = tmem + (uint32_t(warp * 32) << 16);
 
-    constexpr uint32_t kIdescQK = tc5::idesc_f16(kBM, kBN, 0, 0);        // A = Q (K-major), B = K (K-major)
-    constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);   // A = P (K-major), B = V (MN-major)
-
-    const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
-    float m = sink2, l = 1.0f;  // prefill.metal:162
-    uint32_t mma_phase = 0;
-    bool ok = __all_sync(0xffffffffu, wait_bar(bar_q, 0));  // kept warp-uniform: tcgen05.ld/st are warp-wide
-    const uint32_t lane_base = tmem + (uint32_t(warp * 32) << 16);
-
-    for (int kt = 0; kt < n_tiles && ok; kt++) {
-        const int st = kt & 1;
-        // the other stage was last read by the P.V product of tile kt-1, which every thread has waited for
-        if (tid == 0 && kt + 1 < n_tiles) load_kv(kt + 1);
-        ok = __all_sync(0xffffffffu, wait_bar(bar_full0 + 8 * st, (kt >> 1) & 1));
-        if (!ok) break;
-        if (tid == 0) {
+        for (int kt = 0; kt < n_tiles && ok; kt++) {
+            const int st = kt & 1;
+            ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + st), (kt >> 1) & 1));  // warp-uniform for tcgen05.ld
+            if (!ok) break;
             tc5::fence_after_sync();
+            float s[kBN];
+            {
+                uint32_t r0[32], r1[32];
+                tc5::tmem_ld32(lane_base + kColS + st * kBN, r0);
+                tc5::tmem_ld32(lane_base + kColS + st * kBN + 32, r1);
+                tc5::tmem_wait_ld();
 #pragma unroll
-            for (int ks = 0; ks < kHeadDim / 16; ks++) {
-                const uint32_t koff = (ks >> 2) * (kQBytes / 2) + (ks & 3) * 32;
-                const uint32_t kboff = (ks >> 2) * (kKBytes / 2) + (ks & 3) * 32;
-                tc5::mma_f16_ss(tmem + kColS, tc5::smem_desc_sw128(sQ + koff, 16, 1024),
-                                tc5::smem_desc_sw128(sK + st * kKBytes + kboff, 16, 1024), kIdescQK, ks > 0);
+                for (int c = 0; c < 32; c++) {
+                    s[c] = __uint_as_float(r0[c]);
+                    s[c + 32] = __uint_as_float(r1[c]);
+                }
             }
-            tc5::mma_commit(bar_mma);
-        }
-        ok = __all_sync(0xffffffffu, wait_bar(bar_mma, mma_phase));
-        mma_phase ^= 1;
-        if (!ok) break;
-        tc5::fence_after_sync();
-
-        // ---- this thread's row of S: mask, running max, probabilities
-        float s[kBN];
-        {
-            uint32_t r0[32], r1[32];
-            tc5::tmem_ld32(lane_base + kColS, r0);
-            tc5::tmem_ld32(lane_base + kColS + 32, r1);
-            tc5::tmem_wait_ld();
+            const int kbase = klo + kt * kBN;
+            // interior tiles of the band are visible to all 16 positions of the block: no per-element mask
+            const bool need_mask = kbase + kBN - 1 > q_first || (a.is_swa && kbase < q_last - kHist);
+            float mx = -INFINITY;
+            if (need_mask) {
 #pragma unroll
-            for (int c = 0; c < 32; c++) {
-                s[c] = __uint_as_float(r0[c]);
-                s[c + 32] = __uint_as_float(r1[c]);
+                for (int c = 0; c < kBN; c++) {
+                    const int kpos = kbase + c;
+                    const bool vis = kpos <= qpos && (!a.is_swa || qpos - kpos <= kHist);  // prefill.metal:212
+                    s[c] = vis ? s[c] : -INFINITY;
+                    mx = fmaxf(mx, s[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < kBN; c++) mx = fmaxf(mx, s[c]);
             }
-        }
-        const int kbase = klo + kt * kBN;
-        float mx = -INFINITY;
+            // lazy rescale: keep the old reference maximum unless the row maximum outgrew it by more than 2^8
+            float corr = 1.0f;
+            if (kt == 0) {
+                m = fmaxf(m, mx);
+                l = fast_exp2(sink2 - m);  // the sink's share of the denominator under the new maximum
+            } else if (mx > m + 8.0f) {
+                corr = fast_exp2(m - mx);
+                m = mx;
+                l *= corr;
+            }
+            uint32_t pw[kBN / 2];
+            {
+                float sum = 0.f;
 #pragma unroll
-        for (int c = 0; c < kBN; c++) {
-            const int kpos = kbase + c;
-            const bool vis = row_valid && kpos <= qpos && (!a.is_swa || qpos - kpos <= kHist);  // prefill.metal:212
-            s[c] = vis ? s[c] : -INFINITY;
-            mx = fmaxf(mx, s[c]);
+                for (int c = 0; c < kBN; c += 2) {
+                    const float p0 = fast_exp2(s[c] - m), p1 = fast_exp2(s[c + 1] - m);
+                    sum += p0 + p1;
+                    pw[c >> 1] = pack_half2(p0, p1);
+                }
+                l += sum;
+            }
+            if (kt >= 1) {
+                // O and the P buffer belong to the tensor core until the P.V product of tile kt-1 has completed
+                ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (kt - 1) & 1));
+                if (!ok) break;
+                tc5::fence_after_sync();
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll
+                    for (int cb = 0; cb < kHeadDim; cb += 32) {
+                        uint32_t r[32];
+                        tc5::tmem_ld32(lane_base + kColO + cb, r);
+                        tc5::tmem_wait_ld();
+#pragma unroll
+                        for (int c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                        tc5::tmem_st32(lane_base + kColO + cb, r);
+                    }
+                    tc5::tmem_wait_st();
+                }
+            }
+            unsigned char *prow = gen + kOffP + tid * (kBN * 2);
+#pragma unroll
+            for (int ch = 0; ch < kBN / 8; ch++)
+                *reinterpret_cast<uint4 *>(prow + ((ch ^ (tid & 7)) << 4)) =
+                    make_uint4(pw[4 * ch], pw[4 * ch + 1], pw[4 * ch + 2], pw[4 * ch + 3]);
+            tc5::fence_proxy_async();
+            tc5::fence_before_sync();
+            tc5::mbar_arrive(bar(kBarPReady));
         }
-        // lazy rescale: keep the old reference maximum unless the row maximum outgrew it by more than 2^8
-        float corr = 1.0f;
-        if (kt == 0) {
-            m = fmaxf(m, mx);
-            l = fast_exp2(sink2 - m);  // the sink's share of the denominator under the new maximum
-        } else if (mx > m + 8.0f) {
-            corr = fast_exp2(m - mx);
-            m = mx;
-            l *= corr;
-        }
-        if (kt > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (n_tiles - 1) & 1));
+        if (ok) {
+            tc5::fence_after_sync();
+            const float inv_l = 1.0f / l;  // prefill.metal:255-265
+            const size_t o0 = (size_t(t0 + qi) * kNHead + kvh * kGqa + hl) * kHeadDim;
 #pragma unroll
             for (int cb = 0; cb < kHeadDim; cb += 32) {
                 uint32_t r[32];
                 tc5::tmem_ld32(lane_base + kColO + cb, r);
                 tc5::tmem_wait_ld();
+                if (row_valid) {
+                    if (a.out_dtype == kDtypeF32) {
+                        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(a.out) + o0 + cb);
 #pragma unroll
-                for (int c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-                tc5::tmem_st32(lane_base + kColO + cb, r);
-            }
-            tc5::tmem_wait_st();
-        }
-        {
-            float sum = 0.f;
-            unsigned char *prow = gen + kOffP + tid * (kBN * 2);
+                        for (int c = 0; c < 8; c++)
+                            dst[c] = make_float4(__uint_as_float(r[4 * c]) * inv_l, __uint_as_float(r[4 * c + 1]) * inv_l,
+                                                 __uint_as_float(r[4 * c + 2]) * inv_l, __uint_as_float(r[4 * c + 3]) * inv_l);
+                    } else {
+                        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(a.out) + o0 + cb);
 #pragma unroll
-            for (int ch = 0; ch < kBN / 8; ch++) {
-                uint32_t w[4];
+                        for (int c = 0; c < 4; c++) {
+                            uint32_t w[4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float p0 = fast_exp2(s[ch * 8 + 2 * j] - m), p1 = fast_exp2(s[ch * 8 + 2 * j + 1] - m);
-                    sum += p0 + p1;
-                    w[j] = pack_half2(p0, p1);
-                }
-                *reinterpret_cast<uint4 *>(prow + ((ch ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            l += sum;
-        }
-        tc5::fence_proxy_async();
-        tc5::fence_before_sync();
-        __syncthreads();
-        if (tid == 0) {
-            tc5::fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < kBN / 16; ks++) {
-                tc5::mma_f16_ss(tmem + kColO, tc5::smem_desc_sw128(sP + ks * 32, 16, 1024),
-                                tc5::smem_desc_sw128(sV + st * kKBytes + ks * 2048, kKBytes / 2, 1024), kIdescPV,
-                                (kt > 0 || ks > 0));
-            }
-            tc5::mma_commit(bar_mma);
-        }
-        ok = __all_sync(0xffffffffu, wait_bar(bar_mma, mma_phase));
-        mma_phase ^= 1;
-        if (!ok) break;
-        tc5::fence_after_sync();
-    }
-
-    if (ok) {
-        const float inv_l = 1.0f / l;  // prefill.metal:255-265
-        const size_t o0 = (size_t(t0 + qi) * kNHead + kvh * kGqa + hl) * kHeadDim;
-#pragma unroll
-        for (int cb = 0; cb < kHeadDim; cb += 32) {
-            uint32_t r[32];
-            tc5::tmem_ld32(lane_base + kColO + cb, r);
-            tc5::tmem_wait_ld();
-            if (row_valid) {
-                if (a.out_dtype == kDtypeF32) {
-                    float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(a.out) + o0 + cb);
-#pragma unroll
-                    for (int c = 0; c < 8; c++)
-                        dst[c] = make_float4(__uint_as_float(r[4 * c]) * inv_l, __uint_as_float(r[4 * c + 1]) * inv_l,
-                                             __uint_as_float(r[4 * c + 2]) * inv_l, __uint_as_float(r[4 * c + 3]) * inv_l);
-                } else {
-                    uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(a.out) + o0 + cb);
-#pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]) * inv_l,
-                                                                           __uint_as_float(r[8 * c + 2 * j + 1]) * inv_l);
-                            w[j] = *reinterpret_cast<const uint32_t *>(&b);
+                            for (int j = 0; j < 4; j++) {
+                                const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]) * inv_l,
+                                                                               __uint_as_float(r[8 * c + 2 * j + 1]) * inv_l);
+                                w[j] = *reinterpret_cast<const uint32_t *>(&b);
+                            }
+                            dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                        dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
+        } else if ((tid & 31) == 0) {
+            atomicExch(a.error_flag, 1);  // a wait ran out: report, then leave through the normal teardown
         }
-    } else if (tid == 0) {
-        atomicExch(a.error_flag, 1);  // a wait ran out: report, then leave through the normal teardown
     }
     tc5::fence_before_sync();
     __syncthreads();
@@ -443,7 +495,7 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
         (*n_launches)++;
     }
     pa.history_pass = 0;
-    k_prefill_prologue<<<unsigned(((long long)T * 40 + 7) / 8), 256, 0, stream>>>(pa);
+    k_prefill_prologue<<<unsigned(((long long)T * 5 + 7) / 8), 256, 0, stream>>>(pa);
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     (*n_launches)++;
 
@@ -460,7 +512,9 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
     const dim3 grid((T + kQPos - 1) / kQPos, kNHeadKv);
-    k_prefill_attn<<<grid, kBM, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
+    k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*n_launches)++;

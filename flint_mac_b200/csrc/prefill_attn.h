@@ -14,6 +14,7 @@ struct PrefillParams {
     int is_swa, has_rope;
     int p0, n_tok;     // positions p0 .. p0+n_tok-1
     int qkv_dtype, out_dtype;
+    cudaEvent_t ev_attn_begin = nullptr, ev_attn_end = nullptr;  // optional: recorded around the attention kernel alone
 };
 
 // Device scratch that lives with the handle and grows on demand: half-precision staging of the normalised,
