@@ -329,7 +329,7 @@ def run_decode(args):
     checksum = float(out_host.float().abs().mean())
     h.close()
     prefill = None
-    if world == 1 or rank == 0:
+    if not args.skip_prefill and (world == 1 or rank == 0):
         with ClockSampler(local) as clk_pf:
             prefill = measure_prefill(torch, fa, fo, local, iters=30, warmup=5)
         prefill["clocks"] = clk_pf.summary()
@@ -339,7 +339,7 @@ def run_decode(args):
     if rank == 0:
         cores = os.cpu_count() or 1
         t_cpu0 = time.perf_counter()
-        sec_per_seq = cpu_decode_sample(0, 4, CTX, cores, reps=2)
+        sec_per_seq = cpu_decode_sample(0, 1 if args.skip_cpu else 4, CTX, cores, reps=1 if args.skip_cpu else 2)
         cpu_gbs = decode_bytes(1, CTX) / sec_per_seq / 1e9
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -367,18 +367,48 @@ def run_decode(args):
     return line, rank, world
 
 
+def run_prefill_only(args):
+    """`--workload prefill`: the 4000-token prefill as the headline line (single GPU by configuration)."""
+    import torch
+
+    import flint_mac_b200 as fa
+    from oracle import oracle as fo
+
+    rank, world, local = dist_setup(args.gpus)
+    if rank != 0:
+        return
+    with ClockSampler(local) as clk:
+        pf = measure_prefill(torch, fa, fo, local, iters=args.steps, warmup=args.warmup)
+    line = {"metric": "prefill_attn_tflops", "value": pf["tflops"], "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": pf["step_us"] * 1e-3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 tensor-core products (tcgen05 kind::f16), f32 accumulate/softmax",
+            "data": "synthetic", "config": {"workload": pf["workload"], "l2": pf["l2"]},
+            "roofline": {"bound": "tensor", "achieved": pf["tflops"], "peak": pf["peak_tflops"], "unit": "TFLOP/s",
+                         "frac": pf["frac"], "traffic": None, "peak_kind": pf["peak_kind"], "kernel": "k_prefill_attn",
+                         "kernel_us": pf["attn_kernel_us"], "flops_per_launch": pf["algorithmic_flops"]},
+            "e2e": {"value": pf["e2e_tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": pf["h2d_bytes_per_step"],
+                    "d2h_bytes_per_step": pf["d2h_bytes_per_step"], "us_per_step": pf["e2e_us"]},
+            "gpu_launches": 2 * args.steps, "tok_per_s": pf["tok_per_s"], "clocks": clk.summary()}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--skip-prefill", action="store_true", help="decode workload only (profiling runs)")
+    ap.add_argument("--skip-cpu", action="store_true", help="shortest possible CPU baseline sample (profiling runs)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.workload == "prefill":
+        run_prefill_only(args)
         return
     line, rank, world = run_decode(args)
     if rank == 0:

@@ -41,9 +41,18 @@ constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKBytes;
 constexpr int kOffP = kOffV + kStages * kKBytes;
 constexpr int kOffBar = kOffP + kPBytes;
+constexpr int kOutBlockBytes = kQPos * kGqa * 128;  // one 128-byte-wide column block of the output tile
+static_assert(4 * kOutBlockBytes <= kQBytes + kStages * kKBytes, "the output tile reuses the Q and K buffers");
 constexpr int kSmemBytes = kOffBar + 128;  // 114816 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
 
+#ifdef FLINT_PF_TRACE
+#define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 100 && blockIdx.y == 0) a.trace[(slot)] = clock64(); } while (0)
+#else
+#define PF_TRACE(slot) do { } while (0)
+#endif
+
 struct PfArgs {
+    long long *trace;  // debug timeline (only with FLINT_PF_TRACE)
     void *out;
     const float *sinks;
     int *error_flag;
@@ -157,15 +166,15 @@ __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) 
 
 // ------------------------------------------------------------------------------------------------- attention
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
-    // bounded in wall-clock time: ~0.25 s, far beyond anything a healthy launch needs
+    // Bounded: gives up after ~2^29 SM cycles (a quarter of a second), far beyond anything a healthy launch needs.
+    // The cycle counter is SM-local and cheap to read, and it is only looked at every 64 polls.
     if (tc5::mbar_try_wait(bar, parity)) return true;
-    uint64_t t0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    const long long t0 = clock64();
     for (;;) {
-        if (tc5::mbar_try_wait(bar, parity)) return true;
-        uint64_t t1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-        if (t1 - t0 > 250000000ull) return false;
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (tc5::mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 29)) return false;
     }
 }
 
@@ -179,6 +188,7 @@ enum { kBarQ = 0, kBarKFull = 1, kBarVFull = 3, kBarSReady = 5, kBarPReady = 7, 
 __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_v,
+                                                                  const __grid_constant__ CUtensorMap tm_o,
                                                                   const PfArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -194,6 +204,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
     const int tid = threadIdx.x, warp = tid >> 5;
     const int kvh = blockIdx.y;
     const int t0 = blockIdx.x * kQPos;
+    if (tid == 0) PF_TRACE(999);
     const int q_first = a.p0 + t0;
     const int q_last = a.p0 + min(t0 + kQPos, a.n_tok) - 1;
     const int klo = a.is_swa ? max(q_first - kHist, a.key_row0) : 0;
@@ -230,14 +241,17 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                 tc5::tma_load_3d(sV + st * kKBytes, &tm_v, bar(kBarVFull + st), 0, row, kvh);
                 tc5::tma_load_3d(sV + st * kKBytes + kKBytes / 2, &tm_v, bar(kBarVFull + st), 64, row, kvh);
             };
+            constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
+            const uint32_t q_lo = tc5::desc_lo(sQ, 16), k_lo = tc5::desc_lo(sK, 16), p_lo = tc5::desc_lo(sP, 16);
+            const uint32_t v_lo = tc5::desc_lo(sV, kKBytes / 2);
             auto issue_qk = [&](int kt) {
                 const int st = kt & 1;
+                const uint32_t kst = k_lo + uint32_t(st) * (kKBytes >> 4), d = tmem + kColS + st * kBN;
 #pragma unroll
                 for (int ks = 0; ks < kHeadDim / 16; ks++) {
-                    const uint32_t qoff = (ks >> 2) * (kQBytes / 2) + (ks & 3) * 32;
-                    const uint32_t koff = (ks >> 2) * (kKBytes / 2) + (ks & 3) * 32;
-                    tc5::mma_f16_ss(tmem + kColS + st * kBN, tc5::smem_desc_sw128(sQ + qoff, 16, 1024),
-                                    tc5::smem_desc_sw128(sK + st * kKBytes + koff, 16, 1024), kIdescQK, ks > 0);
+                    constexpr uint32_t kQHalf = (kQBytes / 2) >> 4, kKHalf = (kKBytes / 2) >> 4;
+                    tc5::mma_f16_ss_lohi(d, q_lo + (ks >> 2) * kQHalf + (ks & 3) * 2, kst + (ks >> 2) * kKHalf + (ks & 3) * 2,
+                                         kDescHi, kIdescQK, ks > 0);
                 }
                 tc5::mma_commit(bar(kBarSReady + st));
             };
@@ -255,33 +269,43 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
             if (ok) issue_qk(0);
             for (int kt = 0; kt < n_tiles && ok; kt++) {
                 const int st = kt & 1;
+                PF_TRACE(1000 + kt * 8 + 0);
                 if (kt + 1 < n_tiles) {
                     // S[(kt+1)&1] was drained by the softmax of tile kt-1 (its P-ready arrival was waited for below)
                     ok = wait_bar(bar(kBarKFull + (st ^ 1)), ((kt + 1) >> 1) & 1);
                     if (!ok) break;
                     issue_qk(kt + 1);
                 }
+                PF_TRACE(1000 + kt * 8 + 1);
                 if (kt >= 1 && kt + 1 < n_tiles) {
                     // V stage of tile kt-1 is free once its P.V product has completed
                     ok = wait_bar(bar(kBarPvDone), (kt - 1) & 1);
                     if (!ok) break;
                     load_v(kt + 1);
                 }
+                PF_TRACE(1000 + kt * 8 + 2);
                 if (kt + 2 < n_tiles) {
                     // K stage of tile kt is free once Q.K^T of tile kt has completed
                     ok = wait_bar(bar(kBarSReady + st), (kt >> 1) & 1);
                     if (!ok) break;
                     load_k(kt + 2);
                 }
-                ok = wait_bar(bar(kBarPReady), kt & 1) && wait_bar(bar(kBarVFull + st), (kt >> 1) & 1);
+                PF_TRACE(1000 + kt * 8 + 3);
+                ok = wait_bar(bar(kBarPReady), kt & 1);
+                PF_TRACE(1000 + kt * 8 + 4);
+                ok = ok && wait_bar(bar(kBarVFull + st), (kt >> 1) & 1);
                 if (!ok) break;
+                PF_TRACE(1000 + kt * 8 + 5);
                 tc5::fence_after_sync();
+                {
+                    const uint32_t vst = v_lo + uint32_t(st) * (kKBytes >> 4);
 #pragma unroll
-                for (int ks = 0; ks < kBN / 16; ks++)
-                    tc5::mma_f16_ss(tmem + kColO, tc5::smem_desc_sw128(sP + ks * 32, 16, 1024),
-                                    tc5::smem_desc_sw128(sV + st * kKBytes + ks * 2048, kKBytes / 2, 1024), kIdescPV,
-                                    (kt > 0 || ks > 0));
+                    for (int ks = 0; ks < kBN / 16; ks++)
+                        tc5::mma_f16_ss_lohi(tmem + kColO, p_lo + ks * 2, vst + ks * (2048 >> 4), kDescHi, kIdescPV,
+                                             (kt > 0 || ks > 0));
+                }
                 tc5::mma_commit(bar(kBarPvDone));
+                PF_TRACE(1000 + kt * 8 + 6);
             }
             if (!ok) atomicExch(a.error_flag, 1);
         }
@@ -289,15 +313,16 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
         // =========================================================== softmax warps: one query row per thread
         const int hl = tid >> 4, qi = tid & 15;  // row = head-in-group * 16 + position-in-block (the TMA box order)
         const int qpos = q_first + qi;
-        const bool row_valid = t0 + qi < a.n_tok;
         const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
         float m = sink2, l = 1.0f;  // prefill.metal:162
         const uint32_t lane_base = tmem + (uint32_t(warp * 32) << 16);
 
         for (int kt = 0; kt < n_tiles && ok; kt++) {
             const int st = kt & 1;
+            if (tid == 0) PF_TRACE(kt * 8 + 0);
             ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + st), (kt >> 1) & 1));  // warp-uniform for tcgen05.ld
             if (!ok) break;
+            if (tid == 0) PF_TRACE(kt * 8 + 1);
             tc5::fence_after_sync();
             float s[kBN];
             {
@@ -311,6 +336,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                     s[c + 32] = __uint_as_float(r1[c]);
                 }
             }
+            if (tid == 0) PF_TRACE(kt * 8 + 2);
             const int kbase = klo + kt * kBN;
             // interior tiles of the band are visible to all 16 positions of the block: no per-element mask
             const bool need_mask = kbase + kBN - 1 > q_first || (a.is_swa && kbase < q_last - kHist);
@@ -324,8 +350,13 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                     mx = fmaxf(mx, s[c]);
                 }
             } else {
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
 #pragma unroll
-                for (int c = 0; c < kBN; c++) mx = fmaxf(mx, s[c]);
+                for (int c = 0; c < kBN; c += 4) {
+                    m4[0] = fmaxf(m4[0], s[c]); m4[1] = fmaxf(m4[1], s[c + 1]);
+                    m4[2] = fmaxf(m4[2], s[c + 2]); m4[3] = fmaxf(m4[3], s[c + 3]);
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             // lazy rescale: keep the old reference maximum unless the row maximum outgrew it by more than 2^8
             float corr = 1.0f;
@@ -339,15 +370,18 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
             }
             uint32_t pw[kBN / 2];
             {
-                float sum = 0.f;
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                for (int c = 0; c < kBN; c += 2) {
+                for (int c = 0; c < kBN; c += 4) {
                     const float p0 = fast_exp2(s[c] - m), p1 = fast_exp2(s[c + 1] - m);
-                    sum += p0 + p1;
+                    const float p2 = fast_exp2(s[c + 2] - m), p3 = fast_exp2(s[c + 3] - m);
+                    sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
                     pw[c >> 1] = pack_half2(p0, p1);
+                    pw[(c >> 1) + 1] = pack_half2(p2, p3);
                 }
-                l += sum;
+                l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
+            if (tid == 0) PF_TRACE(kt * 8 + 3);
             if (kt >= 1) {
                 // O and the P buffer belong to the tensor core until the P.V product of tile kt-1 has completed
                 ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (kt - 1) & 1));
@@ -366,6 +400,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                     tc5::tmem_wait_st();
                 }
             }
+            if (tid == 0) PF_TRACE(kt * 8 + 4);
             unsigned char *prow = gen + kOffP + tid * (kBN * 2);
 #pragma unroll
             for (int ch = 0; ch < kBN / 8; ch++)
@@ -374,44 +409,59 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
             tc5::fence_proxy_async();
             tc5::fence_before_sync();
             tc5::mbar_arrive(bar(kBarPReady));
+            if (tid == 0) PF_TRACE(kt * 8 + 5);
         }
+        if (tid == 0) PF_TRACE(900);
         if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (n_tiles - 1) & 1));
         if (ok) {
+            // O / l (prefill.metal:255-265) goes out through shared memory: each thread drops its row into a
+            // [16 positions][8 heads][128 B] swizzled tile per 128-byte column block (the Q and K buffers are idle by
+            // now), then one thread hands the tiles to TMA, which writes full lines and clips rows past the prompt.
             tc5::fence_after_sync();
-            const float inv_l = 1.0f / l;  // prefill.metal:255-265
-            const size_t o0 = (size_t(t0 + qi) * kNHead + kvh * kGqa + hl) * kHeadDim;
+            const float inv_l = 1.0f / l;
+            const int R = qi * kGqa + hl;
+            unsigned char *stg = gen + kOffQ + R * 128;
+            const int sw = R & 7;
 #pragma unroll
             for (int cb = 0; cb < kHeadDim; cb += 32) {
                 uint32_t r[32];
                 tc5::tmem_ld32(lane_base + kColO + cb, r);
                 tc5::tmem_wait_ld();
-                if (row_valid) {
-                    if (a.out_dtype == kDtypeF32) {
-                        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(a.out) + o0 + cb);
+                if (a.out_dtype == kDtypeF32) {
+                    unsigned char *blk = stg + (cb / 32) * kOutBlockBytes;
 #pragma unroll
-                        for (int c = 0; c < 8; c++)
-                            dst[c] = make_float4(__uint_as_float(r[4 * c]) * inv_l, __uint_as_float(r[4 * c + 1]) * inv_l,
-                                                 __uint_as_float(r[4 * c + 2]) * inv_l, __uint_as_float(r[4 * c + 3]) * inv_l);
-                    } else {
-                        uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(a.out) + o0 + cb);
+                    for (int c = 0; c < 8; c++)
+                        *reinterpret_cast<float4 *>(blk + ((c ^ sw) << 4)) =
+                            make_float4(__uint_as_float(r[4 * c]) * inv_l, __uint_as_float(r[4 * c + 1]) * inv_l,
+                                        __uint_as_float(r[4 * c + 2]) * inv_l, __uint_as_float(r[4 * c + 3]) * inv_l);
+                } else {
+                    unsigned char *blk = stg + (cb / 64) * kOutBlockBytes;
 #pragma unroll
-                        for (int c = 0; c < 4; c++) {
-                            uint32_t w[4];
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t w[4];
 #pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]) * inv_l,
-                                                                               __uint_as_float(r[8 * c + 2 * j + 1]) * inv_l);
-                                w[j] = *reinterpret_cast<const uint32_t *>(&b);
-                            }
-                            dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                        for (int j = 0; j < 4; j++) {
+                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]) * inv_l,
+                                                                           __uint_as_float(r[8 * c + 2 * j + 1]) * inv_l);
+                            w[j] = *reinterpret_cast<const uint32_t *>(&b);
                         }
+                        *reinterpret_cast<uint4 *>(blk + ((((cb & 32) >> 3) + c) ^ sw) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
+            }
+            tc5::fence_proxy_async();
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four softmax warps only
+            if (tid == 0) {
+                const int n_blk = a.out_dtype == kDtypeF32 ? 4 : 2, x_step = a.out_dtype == kDtypeF32 ? 32 : 64;
+                for (int b = 0; b < n_blk; b++)
+                    tc5::tma_store_3d(&tm_o, sQ + b * kOutBlockBytes, b * x_step, kvh * kGqa, t0);
+                tc5::tma_store_commit_and_wait_read();
             }
         } else if ((tid & 31) == 0) {
             atomicExch(a.error_flag, 1);  // a wait ran out: report, then leave through the normal teardown
         }
     }
+    if (tid == 0) PF_TRACE(901);
     tc5::fence_before_sync();
     __syncthreads();
     if (warp == 0) tc5::tmem_dealloc(tmem, kTmemCols);
@@ -422,6 +472,9 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
+#ifdef FLINT_PF_TRACE
+long long *g_trace_buf = nullptr;
+#endif
 
 // half tensor [n_outer][n_rows][128] viewed as 3-D {128, n_rows, n_outer}, box {64, box_rows, box_outer}
 cudaError_t make_map(CUtensorMap *map, const void *base, int n_rows, int n_outer, int box_rows, int box_outer) {
@@ -432,6 +485,20 @@ cudaError_t make_map(CUtensorMap *map, const void *base, int n_rows, int n_outer
     const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box,
                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+// output [n_tok][32][128] (bf16 or f32) viewed as {128, 32, n_tok}; box = one 128-byte column block x 8 heads x 16 tokens
+cudaError_t make_out_map(CUtensorMap *map, void *base, int n_tok, int out_dtype) {
+    const cuuint64_t es = out_dtype == kDtypeF32 ? 4 : 2;
+    const cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(kNHead), cuuint64_t(n_tok)};
+    const cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * es, cuuint64_t(kQDim) * es};
+    const cuuint32_t box[3] = {cuuint32_t(128 / es), cuuint32_t(kGqa), cuuint32_t(kQPos)};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode(map, out_dtype == kDtypeF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
@@ -499,7 +566,8 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     (*n_launches)++;
 
-    CUtensorMap tm_q, tm_k, tm_v;
+    CUtensorMap tm_q, tm_k, tm_v, tm_o;
+    if ((e = make_out_map(&tm_o, p.out, T, p.out_dtype)) != cudaSuccess) return e;
     if ((e = make_map(&tm_q, q_st, T, kNHead, kQPos, kGqa)) != cudaSuccess) return e;
     const void *kb = p.is_swa ? static_cast<const void *>(k_st) : static_cast<const void *>(p.k_cache);
     const void *vb = p.is_swa ? static_cast<const void *>(v_st) : static_cast<const void *>(p.v_cache);
@@ -508,18 +576,35 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     if ((e = make_map(&tm_v, vb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
 
     PfArgs a{};
+    a.trace = nullptr;
+#ifdef FLINT_PF_TRACE
+    {
+        static long long *trace_buf = nullptr;  // debug builds only: 2048 slots, read back by the trace tool
+        if (!trace_buf) { cudaMalloc(&trace_buf, 2048 * sizeof(long long)); }
+        cudaMemsetAsync(trace_buf, 0, 2048 * sizeof(long long), stream);
+        a.trace = trace_buf;
+        g_trace_buf = trace_buf;
+    }
+#endif
     a.out = p.out; a.sinks = p.sinks; a.error_flag = err_flag; a.out_dtype = p.out_dtype;
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
     const dim3 grid((T + kQPos - 1) / kQPos, kNHeadKv);
     if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
-    k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
     if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*n_launches)++;
     return cudaSuccess;
 }
+
+#ifdef FLINT_PF_TRACE
+extern "C" int flint_pf_trace_read(long long *out) {
+    if (!g_trace_buf) return -1;
+    return cudaMemcpy(out, g_trace_buf, 2048 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 cudaError_t prefill_error_flag(const PrefillWorkspace &ws, int *flag) {
     *flag = 0;
