@@ -392,13 +392,213 @@ def run_prefill_only(args):
     print(json.dumps(line), flush=True)
 
 
+def run_longctx(args):
+    """`--workload longctx`: one 131072-token sequence on a full-attention layer, its key range cut contiguously over
+    the ranks.  Every rank scans its range (split-K inside the GPU), the per-rank partial (O, m, l) records are
+    all-gathered with NCCL and merged with the sink by flint_attn_combine_dev.  Several copies of the sequence are
+    rotated through so that each step's keys come from HBM, not L2."""
+    import torch
+
+    import flint_mac_b200 as fa
+    from flint_mac_b200 import dist as fdist
+    from oracle import oracle as fo
+
+    rank, world, local = dist_setup(args.gpus)
+    hbm_peak, _, peak_kind = measured_peaks()
+    S = 131072
+    total = args.warmup + args.steps
+    n_ctx = S + 64
+    per_gpu_bytes = KV_BYTES_PER_KEY * S // world
+    copies = max(2, -(-(320 << 20) // per_gpu_bytes))
+    h = fa.Attn([False], [True], copies, n_ctx, device=local, kv_rank=rank, kv_ranks=world)
+    h.set_layer(0, *fo.layer_weights(0, 0))
+    n_slots = h.n_slots(0)
+    gen = torch.Generator(device="cuda").manual_seed(99 + rank)
+    for which in (0, 1):
+        as_tensor(torch, h.kv_dev(0, which), copies * 4 * n_slots * 128, torch.float16).normal_(generator=gen)
+    g2 = torch.Generator(device="cuda").manual_seed(7)  # same rows on every rank
+    qkv = torch.randn(total, 1, QKV_DIM, generator=g2, device="cuda").to(torch.bfloat16)
+    out = torch.empty(1, OUT_DIM, device="cuda", dtype=torch.bfloat16)
+    part = torch.empty(1, 32, 130, device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+    for c in range(copies):
+        h.set_pos(c, S)
+
+    def step(i):
+        c = i % copies
+        if world == 1:
+            h.decode_dev(0, [c], qkv[i], fa.BF16, out, fa.BF16, stream)
+        else:
+            h.decode_partial_dev(0, [c], qkv[i], fa.BF16, part, stream)
+            gathered = fdist.gather_partials(part)
+            h.combine_dev(0, 1, world, gathered, out, fa.BF16, stream)
+
+    for i in range(args.warmup):
+        step(i)
+    barrier(world)
+    h.set_timing(True)
+    launches0 = h.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        ev1.record()
+        barrier(world)
+    ms = max_over_ranks(ev0.elapsed_time(ev1), world) / args.steps
+    kernel_ms, n_timed = h.kernel_ms()
+    h.set_timing(False)
+    launches = h.launch_count() - launches0
+    step_bytes = decode_bytes(1, S)
+    kernel_us = kernel_ms / max(n_timed, 1) * 1e3
+    h.check()
+    h.close()
+    if rank == 0:
+        per_gpu = step_bytes / world
+        line = {"metric": "decode_attn_hbm_gbs", "value": step_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16 KV, f16 tensor-core products, f32 accumulate/softmax",
+                "data": "synthetic",
+                "config": {"workload": "long-context decode: 1 sequence x 131072 cached tokens, full layer, KV range "
+                                       "sharded over the ranks, partial (O,m,l) all-gathered (NCCL) and merged",
+                           "kv_copies_rotated": copies, "l2": "rotating over KV copies larger than L2 in total"},
+                "tok_per_s": 1.0 / (ms * 1e-3), "us_per_token": ms * 1e3,
+                "roofline": {"bound": "hbm", "achieved": per_gpu / (kernel_us * 1e-6) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                             "frac": per_gpu / (kernel_us * 1e-6) / 1e9 / hbm_peak, "traffic": None,
+                             "peak_kind": f"of {peak_kind}", "kernel": "k_decode_attn (this rank's key range)",
+                             "kernel_us": kernel_us, "bytes_per_launch": per_gpu},
+                "merge_us": ms * 1e3 - kernel_us, "gpu_launches": launches, "clocks": clk.summary()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def run_ragged(args):
+    """`--workload ragged`: one decode step over a 4-layer stack (3 sliding-window ring layers + 1 full layer) for
+    256 sequences whose context lengths are drawn uniformly from 1..32768 (numpy default_rng(7)); a quarter of them
+    were first rolled back by 1..600 tokens (the > 511 ones re-prefill 512 tokens into the rings).  Sequences are
+    placed on ranks by KV bytes (greedy LPT); no collective on the data path."""
+    import torch
+
+    import flint_mac_b200 as fa
+    from flint_mac_b200 import shard
+    from oracle import oracle as fo
+
+    rank, world, local = dist_setup(args.gpus)
+    hbm_peak, _, peak_kind = measured_peaks()
+    rng = np.random.default_rng(7)
+    n_seq = 256
+    ctx_all = [int(x) for x in rng.integers(1, 32769, n_seq)]
+    rolled = rng.random(n_seq) < 0.25
+    back_all = [int(b) if r else 0 for b, r in zip(rng.integers(1, 601, n_seq), rolled)]
+    owned = shard.balance_by_kv_bytes(ctx_all, world, n_full_layers=1, n_swa_layers=3)[rank]
+    ctx = [ctx_all[i] for i in owned]
+    back = [min(back_all[i], ctx_all[i]) for i in owned]
+    n_loc = len(owned)
+    total = args.warmup + args.steps
+    n_ctx = 32768 + total + 8
+    is_swa, has_rope = [True, True, True, False], [True, True, True, False]
+    h = fa.Attn(is_swa, has_rope, n_loc, n_ctx, device=local)
+    for il in range(4):
+        h.set_layer(il, *fo.layer_weights(0, il))
+    gen = torch.Generator(device="cuda").manual_seed(500 + rank)
+    for il in range(4):
+        for which in (0, 1):
+            as_tensor(torch, h.kv_dev(il, which), n_loc * 4 * h.n_slots(il) * 128, torch.float16).normal_(generator=gen)
+    seqs = list(range(n_loc))
+    stream = torch.cuda.current_stream().cuda_stream
+    # ---- rollback phase (untimed for the headline; its cost is reported on its own)
+    for s in seqs:
+        h.set_pos(s, ctx[s])
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_recompute = 0
+    pf_rows = torch.randn(512, QKV_DIM, generator=gen, device="cuda").to(torch.bfloat16)
+    pf_out = torch.empty(512, OUT_DIM, device="cuda", dtype=torch.bfloat16)
+    for s in seqs:
+        if back[s] == 0:
+            continue
+        p = ctx[s] - back[s]
+        restart = fa.rollback_restart(ctx[s], p)
+        assert h.truncate(s, restart) == 0
+        if restart < p:  # rolled back by more than 511: rewrite the rings from restart (server/src/main.rs:96-100)
+            for il in range(3):
+                h.prefill_dev(il, s, p - restart, pf_rows, fa.BF16, pf_out, fa.BF16, stream)
+            h.advance([s], p - restart)
+            n_recompute += 1
+        ctx[s] = p
+    torch.cuda.synchronize()
+    rollback_ms = (time.perf_counter() - t0) * 1e3
+    qkv = torch.randn(4, n_loc, QKV_DIM, generator=gen, device="cuda").to(torch.bfloat16)
+    out = torch.empty(n_loc, OUT_DIM, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        for il in range(4):
+            h.decode_dev(il, seqs, qkv[il], fa.BF16, out, fa.BF16, stream)
+        h.advance(seqs, 1)
+
+    def step_bytes(extra):
+        b = 0
+        for c in ctx:
+            c = c + extra
+            b += KV_BYTES_PER_KEY * (c + 3 * min(c, 512)) + 4 * (QKV_DIM * 2 + 2 * 512 * 2 + OUT_DIM * 2)
+        return b
+
+    for i in range(args.warmup):
+        step()
+    barrier(world)
+    h.set_timing(True)
+    launches0 = h.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        ev0.record()
+        for i in range(args.steps):
+            step()
+        ev1.record()
+        barrier(world)
+    ms = max_over_ranks(ev0.elapsed_time(ev1), world) / args.steps
+    kernel_ms, n_timed = h.kernel_ms()
+    h.set_timing(False)
+    launches = h.launch_count() - launches0
+    my_bytes = sum(step_bytes(args.warmup + i) for i in range(args.steps)) / args.steps
+    all_bytes = sum_over_ranks(my_bytes, world)
+    max_bytes = max_over_ranks(my_bytes, world)
+    h.check()
+    h.close()
+    if rank == 0:
+        kernel_step_us = kernel_ms / args.steps * 1e3
+        line = {"metric": "decode_attn_hbm_gbs", "value": all_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16 KV, f16 tensor-core products, f32 accumulate/softmax",
+                "data": "synthetic",
+                "config": {"workload": "ragged serving mix: 256 sequences, context 1..32768 (numpy default_rng(7)), one decode "
+                                       "step over 3 SWA ring layers + 1 full layer, 25% rolled back by 1..600 tokens first",
+                           "placement": "greedy LPT by KV bytes", "l2": "inputs larger than L2"},
+                "tok_per_s": n_seq / (ms * 1e-3), "bytes_per_step_all_ranks": all_bytes,
+                "load_imbalance": max_bytes * world / all_bytes,
+                "roofline": {"bound": "hbm", "achieved": my_bytes / (kernel_step_us * 1e-6) / 1e9, "peak": hbm_peak,
+                             "unit": "GB/s", "frac": my_bytes / (kernel_step_us * 1e-6) / 1e9 / hbm_peak, "traffic": None,
+                             "peak_kind": f"of {peak_kind}", "kernel": "k_decode_attn (4 launches per step, rank 0)",
+                             "kernel_us": kernel_step_us, "bytes_per_launch": my_bytes},
+                "rollback": {"sequences_rolled_back_rank0": int(sum(1 for b in back if b)), "ring_recomputes_rank0": n_recompute,
+                             "wall_ms_rank0": rollback_ms},
+                "gpu_launches": launches, "clocks": clk.summary()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "ragged"])
     ap.add_argument("--skip-prefill", action="store_true", help="decode workload only (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="shortest possible CPU baseline sample (profiling runs)")
     args = ap.parse_args()
@@ -409,6 +609,12 @@ def main():
         return
     if args.workload == "prefill":
         run_prefill_only(args)
+        return
+    if args.workload == "longctx":
+        run_longctx(args)
+        return
+    if args.workload == "ragged":
+        run_ragged(args)
         return
     line, rank, world = run_decode(args)
     if rank == 0:

@@ -99,7 +99,7 @@ def _ptr(x) -> int:
     return int(x)
 
 
-def plan_decode(pos: Sequence[int], is_swa: bool, kv_lo: int = 0, kv_hi: int = 2**31 - 1, target_items: int = 1184):
+def plan_decode(pos: Sequence[int], is_swa: bool, kv_lo: int = 0, kv_hi: int = 2**31 - 1, target_items: int = 296):
     """Host-only: the decode work list as an int32 array [n_items][8] =
     (token, kv_head, j0, j1, fold_new_token, split, n_split, first_partial)."""
     lib = load_library()

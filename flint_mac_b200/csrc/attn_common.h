@@ -20,6 +20,8 @@ constexpr int kSwaRing = 1024;
 constexpr float kRmsEps = 1e-6f;
 constexpr float kRopeTheta = 10000.0f;
 constexpr int kPartialDim = kHeadDim + 2;      // acc[128], m, l
+constexpr int kRecStride = 132;                // floats between split-K scratch records (16-byte aligned rows)
+constexpr int kMergeFan = 16;                  // splits folded by one CTA in the first merge level
 
 constexpr int kDtypeF32 = 0;
 constexpr int kDtypeBf16 = 1;
@@ -35,8 +37,8 @@ struct DecItem {
     int32_t split;     // index of this item among the n_split items of its (tok, kvh) group
     int32_t n_split;
     int32_t part0;     // first partial record of the group in the scratch buffer
-    int32_t group;     // ticket counter index
-    int32_t pad;
+    int32_t group;     // second-level ticket counter index (one per (tok, kvh) group)
+    int32_t sub0;      // first first-level ticket / second-level record of the group (one per run of kMergeFan splits)
 };
 static_assert(sizeof(DecItem) == 48, "DecItem is uploaded as raw bytes");
 
@@ -47,8 +49,10 @@ struct DecParams {
     float *partial_out;     // [n][32][130] (mode 1: this device's keys only, no sink)
     const float *q_norm, *k_norm, *sinks, *inv_freq;
     __half *k_cache, *v_cache;  // [max_seqs][4][n_slots][128]
-    float *scratch;         // split-K partial records [..][8][130]
-    int *tickets;           // one counter per (tok, kvh) group, zero between launches
+    float *scratch;         // split-K partial records [..][8][kRecStride]
+    float *scratch2;        // second-level records, one per run of kMergeFan splits
+    int *tickets;           // one arrival counter per run of kMergeFan splits; all counters are zero between launches
+    int *tickets2;          // one arrival counter per (tok, kvh) group
     long long seq_stride;   // halves between consecutive sequences = 4 * n_slots * 128
     int n_slots;
     uint32_t slot_mask;     // 1023 on ring layers, 0xFFFFFFFF otherwise

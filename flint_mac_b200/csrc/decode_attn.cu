@@ -87,6 +87,40 @@ __device__ __forceinline__ void store_out(void *out, int dtype, size_t idx, floa
     else static_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
 }
 
+struct Merged {
+    float M, L;
+    float a[8];
+};
+
+// Fold n partial records of one head (fused.metal:332-350): M = max m_s (and the sink), L = sum l_s e^(m_s - M)
+// (+ e^(sink - M)), a = sum acc_s e^(m_s - M).  `rec` points at record 0 of this thread's head; consecutive records
+// of the same head are kGqa * kRecStride floats apart.  The thread owns dims [d0, d0 + 8).  Loads are independent
+// across records, so the unrolled loops keep many of them in flight.
+__device__ __forceinline__ Merged merge_records(const float *rec, int n, int d0, bool with_sink, float sink) {
+    constexpr int kStep = kGqa * kRecStride;
+    Merged r;
+    float M = with_sink ? sink : -INFINITY;
+#pragma unroll 8
+    for (int s = 0; s < n; s++) M = fmaxf(M, __ldcg(rec + size_t(s) * kStep + kHeadDim));
+    float L = with_sink ? __expf(sink - M) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) r.a[j] = 0.f;
+#pragma unroll 8
+    for (int s = 0; s < n; s++) {
+        const float *q = rec + size_t(s) * kStep;
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(q + kHeadDim));
+        const float4 x = __ldcg(reinterpret_cast<const float4 *>(q + d0));
+        const float4 y = __ldcg(reinterpret_cast<const float4 *>(q + d0 + 4));
+        const float c = ml.y == 0.f ? 0.f : __expf(ml.x - M);  // an empty part has m = -inf, l = 0 (fused.metal:344)
+        L += ml.y * c;
+        r.a[0] += x.x * c; r.a[1] += x.y * c; r.a[2] += x.z * c; r.a[3] += x.w * c;
+        r.a[4] += y.x * c; r.a[5] += y.y * c; r.a[6] += y.z * c; r.a[7] += y.w * c;
+    }
+    r.M = M;
+    r.L = L;
+    return r;
+}
+
 __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DecSmem &sm = *reinterpret_cast<DecSmem *>(smem_raw);
@@ -264,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) 
 
     const int d = tid;  // this thread owns one of the 128 output dims for all 8 heads
     const bool direct = it.n_split == 1;
-    float *rec_base = direct ? nullptr : p.scratch + (size_t(it.part0) + it.split) * kGqa * kPartialDim;
+    float *rec_base = direct ? nullptr : p.scratch + (size_t(it.part0) + it.split) * kGqa * kRecStride;
 #pragma unroll 1
     for (int h = 0; h < kGqa; h++) {
         float M = -INFINITY;
@@ -286,49 +320,76 @@ __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) 
             const float Mf = fmaxf(M, sink2), cs = fast_exp2(M - Mf);
             store_out(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + d,
                       A * cs / (L * cs + fast_exp2(sink2 - Mf)));
+        } else if (direct) {
+            // this device's only record for the token: {acc[128], m, l}, m in natural-log units (fused.metal:324-327)
+            float *rec = p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim;
+            rec[d] = A;
+            if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
         } else {
-            // partial record {acc[128], m, l}, m in natural-log units (fused.metal:324-327)
-            float *rec = direct ? p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim
-                                : rec_base + size_t(h) * kPartialDim;
+            float *rec = rec_base + size_t(h) * kRecStride;
             rec[d] = A;
             if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
         }
     }
     if (direct) return;
 
-    // ---- split-K: the last CTA of the group to arrive merges all of its records (fused.metal:332-350) -------------
+    // ---- split-K merge (fused.metal:332-350), done by whichever CTA finishes last -- no second launch, no waiting.
+    // Two levels, so that a long sequence cut into hundreds of splits is not merged by a single CTA: the last CTA of
+    // each run of 16 splits folds those records into one; the last of those to finish folds the runs and the sink.
+    const int sub = it.split / kMergeFan, n_sub = (it.n_split + kMergeFan - 1) / kMergeFan;
+    const int sub_size = min(kMergeFan, it.n_split - sub * kMergeFan);
     __threadfence();
     __syncthreads();
-    if (tid == 0) sm.is_last = (atomicAdd(&p.tickets[it.group], 1) == it.n_split - 1);
+    if (tid == 0) sm.is_last = (atomicAdd(&p.tickets[it.sub0 + sub], 1) == sub_size - 1);
     __syncthreads();
     if (!sm.is_last) return;
     __threadfence();
-    const float *grp = p.scratch + size_t(it.part0) * kGqa * kPartialDim;
-#pragma unroll 1
-    for (int h = 0; h < kGqa; h++) {
-        const int head = it.kvh * kGqa + h;
-        const float sink = p.sinks[head];
-        float M = p.mode == 0 ? sink : -INFINITY;
-        for (int s = 0; s < it.n_split; s++) M = fmaxf(M, __ldcg(grp + (size_t(s) * kGqa + h) * kPartialDim + kHeadDim));
-        float L = p.mode == 0 ? __expf(sink - M) : 0.f;
-        float A = 0.f;
-        for (int s = 0; s < it.n_split; s++) {
-            const float *rec = grp + (size_t(s) * kGqa + h) * kPartialDim;
-            const float ls = __ldcg(rec + kHeadDim + 1);
-            if (ls == 0.f) continue;
-            const float c = __expf(__ldcg(rec + kHeadDim) - M);
-            L += ls * c;
-            A += __ldcg(rec + d) * c;
-        }
-        if (p.mode == 0) {
-            store_out(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + d, A / L);
-        } else {
-            float *rec = p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim;
-            rec[d] = A;
-            if (d == 0) { rec[kHeadDim] = M; rec[kHeadDim + 1] = L; }
-        }
+    if (tid == 0) p.tickets[it.sub0 + sub] = 0;  // ready for the next launch
+
+    const int mh = tid >> 4, md = (tid & 15) * 8;  // merge layout: 16 threads per head, 8 dims per thread
+    const int head = it.kvh * kGqa + mh;
+    const float sink = p.sinks[head];
+    const float *lvl1 = p.scratch + ((size_t(it.part0) + sub * kMergeFan) * kGqa + mh) * kRecStride;
+    Merged r;
+    if (n_sub == 1) {
+        r = merge_records(lvl1, sub_size, md, p.mode == 0, sink);
+    } else {
+        r = merge_records(lvl1, sub_size, md, false, 0.f);
+        float *rec2 = p.scratch2 + ((size_t(it.sub0) + sub) * kGqa + mh) * kRecStride;
+        *reinterpret_cast<float4 *>(rec2 + md) = make_float4(r.a[0], r.a[1], r.a[2], r.a[3]);
+        *reinterpret_cast<float4 *>(rec2 + md + 4) = make_float4(r.a[4], r.a[5], r.a[6], r.a[7]);
+        if (md == 0) { rec2[kHeadDim] = r.M; rec2[kHeadDim + 1] = r.L; }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) sm.is_last = (atomicAdd(&p.tickets2[it.group], 1) == n_sub - 1);
+        __syncthreads();
+        if (!sm.is_last) return;
+        __threadfence();
+        if (tid == 0) p.tickets2[it.group] = 0;
+        r = merge_records(p.scratch2 + (size_t(it.sub0) * kGqa + mh) * kRecStride, n_sub, md, p.mode == 0, sink);
     }
-    if (tid == 0) p.tickets[it.group] = 0;  // ready for the next launch
+    if (p.mode == 0) {
+        const float inv = 1.0f / r.L;
+        const size_t o = size_t(it.tok) * kQDim + head * kHeadDim + md;
+        if (p.out_dtype == kDtypeF32) {
+            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + o);
+            dst[0] = make_float4(r.a[0] * inv, r.a[1] * inv, r.a[2] * inv, r.a[3] * inv);
+            dst[1] = make_float4(r.a[4] * inv, r.a[5] * inv, r.a[6] * inv, r.a[7] * inv);
+        } else {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const __nv_bfloat162 b = __floats2bfloat162_rn(r.a[2 * j] * inv, r.a[2 * j + 1] * inv);
+                w[j] = *reinterpret_cast<const uint32_t *>(&b);
+            }
+            *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    } else {
+        float *rec = p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim;  // 130-float public record
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) *reinterpret_cast<float2 *>(rec + md + j) = make_float2(r.a[j], r.a[j + 1]);
+        if (md == 0) { rec[kHeadDim] = r.M; rec[kHeadDim + 1] = r.L; }
+    }
 }
 
 // Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.

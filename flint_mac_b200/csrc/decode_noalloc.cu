@@ -8,7 +8,7 @@
 // The caller passes every input and output (rows, caches, layer parameters) as device pointers it owns, and the
 // only memory the kernel needs beyond those -- the work list, the split-K partial records, the per-group arrival
 // counters and the RoPE frequency table -- lives in the fixed array below, which is part of the loaded library
-// image on every GPU that loads it (about 8.4 MiB per GPU until the process exits).
+// image on every GPU that loads it (about 10 MiB per GPU until the process exits).
 //
 // It runs the same kernel as flint_attn_decode_dev (k_decode_attn), with the same planner.
 #include <climits>
@@ -25,14 +25,21 @@ namespace {
 
 constexpr int kMaxTokens = FLINT_ATTN_NOALLOC_MAX_TOKENS;  // 64
 constexpr int kMaxItems = FLINT_ATTN_NOALLOC_MAX_ITEMS;    // 2048
-constexpr int kTargetItems = 1184;                         // what the handle uses on a 148-SM part
+constexpr int kTargetItems = 296;                          // what the handle uses on a 148-SM part
 
-// Layout of the fixed scratch (byte offsets, each a multiple of 256).
-constexpr size_t kOffFreq = 0;                                             // float[64]
-constexpr size_t kOffTickets = 256;                                        // int[kMaxTokens * 4]
-constexpr size_t kOffItems = kOffTickets + sizeof(int) * kMaxTokens * kNHeadKv;           // DecItem[kMaxItems]
-constexpr size_t kOffRecords = (kOffItems + sizeof(DecItem) * kMaxItems + 255) / 256 * 256;  // float[kMaxItems][8][130]
-constexpr size_t kScratchBytes = kOffRecords + sizeof(float) * kMaxItems * kGqa * kPartialDim;
+// Layout of the fixed scratch (byte offsets, each a multiple of 256).  A group of n splits is merged in runs of
+// kMergeFan, so it needs ceil(n / kMergeFan) run counters / second-level records: at most kMaxRuns in total.
+constexpr int kMaxGroups = kMaxTokens * kNHeadKv;
+constexpr int kMaxRuns = kMaxItems / kMergeFan + kMaxGroups;
+constexpr size_t kAlign = 256;
+constexpr size_t up(size_t x) { return (x + kAlign - 1) / kAlign * kAlign; }
+constexpr size_t kOffFreq = 0;                                                        // float[64]
+constexpr size_t kOffTickets = 256;                                                   // int[kMaxRuns + kMaxGroups]
+constexpr size_t kTicketBytes = sizeof(int) * (kMaxRuns + kMaxGroups);
+constexpr size_t kOffItems = up(kOffTickets + kTicketBytes);                          // DecItem[kMaxItems]
+constexpr size_t kOffRecords = up(kOffItems + sizeof(DecItem) * kMaxItems);           // float[kMaxItems][8][kRecStride]
+constexpr size_t kOffRecords2 = up(kOffRecords + sizeof(float) * kMaxItems * kGqa * kRecStride);  // float[kMaxRuns][8][kRecStride]
+constexpr size_t kScratchBytes = kOffRecords2 + sizeof(float) * kMaxRuns * kGqa * kRecStride;
 
 // In host code this name is only a handle for cudaGetSymbolAddress: it is NOT a device address and must never be
 // handed to a kernel as a pointer.
@@ -65,7 +72,7 @@ const char *setup_device(int dev) {
     unsigned char *base = static_cast<unsigned char *>(ptr);
     if (cudaMemcpy(base + kOffFreq, freq, sizeof(freq), cudaMemcpyHostToDevice) != cudaSuccess)
         return "could not initialise the RoPE table in the fixed scratch array";
-    if (cudaMemset(base + kOffTickets, 0, sizeof(int) * kMaxTokens * kNHeadKv) != cudaSuccess)
+    if (cudaMemset(base + kOffTickets, 0, kTicketBytes) != cudaSuccess)
         return "could not clear the arrival counters in the fixed scratch array";
     if (decode_kernel_setup() != cudaSuccess) return "could not set the decode kernel's shared-memory size";
     if (cudaDeviceSynchronize() != cudaSuccess) return "device error during set-up";
@@ -126,6 +133,15 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
         fail(err, err_len, msg);
         return -1;
     }
+    // Run counters / second-level records are handed out in group order, like the partial records.
+    static int32_t group_splits[kMaxGroups], group_sub0[kMaxGroups];
+    for (int g = 0; g < n * kNHeadKv; g++) group_splits[g] = 1;
+    for (int i = 0; i < n_items; i++) group_splits[g_plan[8 * i] * kNHeadKv + g_plan[8 * i + 1]] = g_plan[8 * i + 6];
+    int n_runs = 0;
+    for (int g = 0; g < n * kNHeadKv; g++) {
+        group_sub0[g] = n_runs;
+        if (group_splits[g] > 1) n_runs += (group_splits[g] + kMergeFan - 1) / kMergeFan;
+    }
     for (int i = 0; i < n_items; i++) {
         const int32_t *r = g_plan + 8 * i;
         DecItem &it = g_items_host[i];
@@ -133,6 +149,7 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
         it.tok = r[0]; it.seq = r[0]; it.kvh = r[1]; it.pos = pos[r[0]];
         it.j0 = r[2]; it.j1 = r[3]; it.fold = r[4]; it.split = r[5]; it.n_split = r[6]; it.part0 = r[7];
         it.group = r[0] * kNHeadKv + r[1];
+        it.sub0 = group_sub0[it.group];
     }
     unsigned char *base = g_state[dev].base;
     cudaStream_t st = cudaStream_t(cuda_stream);
@@ -143,7 +160,7 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
         return -1;
     }
     // The counters must start at zero.  The kernel leaves them at zero, but a launch that failed part-way would not.
-    if (cudaMemsetAsync(base + kOffTickets, 0, sizeof(int) * kMaxTokens * kNHeadKv, st) != cudaSuccess) {
+    if (cudaMemsetAsync(base + kOffTickets, 0, kTicketBytes, st) != cudaSuccess) {
         fail(err, err_len, "flint_attn_decode_noalloc_dev: could not clear the arrival counters");
         return -1;
     }
@@ -157,7 +174,9 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
     dp.k_cache = static_cast<__half *>(k_cache_dev);
     dp.v_cache = static_cast<__half *>(v_cache_dev);
     dp.scratch = reinterpret_cast<float *>(base + kOffRecords);
+    dp.scratch2 = reinterpret_cast<float *>(base + kOffRecords2);
     dp.tickets = reinterpret_cast<int *>(base + kOffTickets);  // left at zero by the kernel after every launch
+    dp.tickets2 = dp.tickets + kMaxRuns;
     dp.seq_stride = (long long)kNHeadKv * n_slots * kHeadDim;
     dp.n_slots = n_slots;
     dp.slot_mask = is_swa ? uint32_t(kSwaRing - 1) : 0xFFFFFFFFu;

@@ -45,10 +45,13 @@ constexpr int kRing = 4;  // work lists in flight
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 // Own split policy.  The reference's (src/engine.mm:742-743: at most 32 splits of at least 256 keys) fills an
-// M5; a B200 wants a few work items per CTA slot on each of its 148 SMs, whatever the batch looks like, so the
-// chunk length is derived from the total number of cached key rows of the whole launch.
+// M5.  On a B200 every work item pays a few microseconds of start-up and merge, so the launch aims for ONE wave:
+// about as many items as there are CTA slots (2 per SM), each as long as possible.  The chunk length is the total
+// number of cached key rows of the launch divided by the slots; a (token, KV head) group gets round(keys / chunk)
+// splits (at least one), so a batch of equally long sequences is not cut in two just because it is a little longer
+// than the chunk.
 void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi, int target_items,
-                 std::vector<DecItem> &items, int &n_groups, int &n_records) {
+                 std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs) {
     items.clear();
     long long total = 0;
     std::vector<int> lo(n), hi(n);
@@ -63,15 +66,19 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
     const int chunk = round_up(int(std::max<long long>(256, (total + target_items - 1) / target_items)), 64);
     n_groups = n * kNHeadKv;
     n_records = 0;
+    n_subs = 0;
     for (int i = 0; i < n; i++) {
         const int nk = hi[i] - lo[i];
         const bool own_new = kv_lo <= pos[i] && pos[i] < kv_hi;
-        int n_split = std::max(1, (nk + chunk - 1) / chunk);
+        int n_split = std::max(1, (nk + chunk / 2) / chunk);
         const int per = std::max(64, round_up((nk + n_split - 1) / n_split, 64));
         n_split = std::max(1, (nk + per - 1) / per);
         for (int kvh = 0; kvh < kNHeadKv; kvh++) {
-            const int part0 = n_records;
-            if (n_split > 1) n_records += n_split;
+            const int part0 = n_records, sub0 = n_subs;
+            if (n_split > 1) {
+                n_records += n_split;
+                n_subs += (n_split + kMergeFan - 1) / kMergeFan;
+            }
             for (int s = 0; s < n_split; s++) {
                 DecItem it{};
                 it.tok = i;
@@ -85,6 +92,7 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
                 it.n_split = n_split;
                 it.part0 = part0;
                 it.group = i * kNHeadKv + kvh;
+                it.sub0 = sub0;
                 items.push_back(it);
             }
         }
@@ -102,8 +110,8 @@ struct flint_attn {
     std::vector<Layer> layers;
     std::vector<int32_t> pos;
     float *inv_freq = nullptr;
-    float *scratch = nullptr;
-    size_t scratch_recs = 0;
+    float *scratch = nullptr, *scratch2 = nullptr;
+    size_t scratch_recs = 0, scratch2_recs = 0;
     int *tickets = nullptr;
     size_t n_tickets = 0;
     // pinned host staging for work lists + matching device buffers, reused round-robin behind events
@@ -128,7 +136,7 @@ struct flint_attn {
         for (auto &L : layers) {
             cudaFree(L.k); cudaFree(L.v); cudaFree(L.q_norm); cudaFree(L.k_norm); cudaFree(L.sinks);
         }
-        cudaFree(inv_freq); cudaFree(scratch); cudaFree(tickets); cudaFree(io_dev);
+        cudaFree(inv_freq); cudaFree(scratch); cudaFree(scratch2); cudaFree(tickets); cudaFree(io_dev);
         for (int i = 0; i < kRing; i++) {
             if (ring_host[i]) cudaFreeHost(ring_host[i]);
             cudaFree(ring_dev[i]);
@@ -200,22 +208,25 @@ struct flint_attn {
             if (ring_dev[i] == dev) CK(cudaEventRecord(ring_ev[i], st));
     }
 
-    void ensure_scratch(int n_records, int n_groups) {
-        if (size_t(n_records) > scratch_recs) {
+    void ensure_scratch(int n_records, int n_subs, int n_groups) {
+        auto grow = [&](float *&buf, size_t &have, size_t need, size_t floor_recs) {
+            if (need <= have) return;
             CK(cudaDeviceSynchronize());  // earlier launches may still be using the old buffer
-            cudaFree(scratch);
-            scratch = nullptr;
-            scratch_recs = 0;
-            const size_t recs = std::max<size_t>(size_t(n_records) * 2, 4096);
-            CK(cudaMalloc(&scratch, recs * kGqa * kPartialDim * sizeof(float)));
-            scratch_recs = recs;
-        }
-        if (size_t(n_groups) > n_tickets) {
+            cudaFree(buf);
+            buf = nullptr;
+            have = 0;
+            const size_t recs = std::max<size_t>(need * 2, floor_recs);
+            CK(cudaMalloc(&buf, recs * kGqa * kRecStride * sizeof(float)));
+            have = recs;
+        };
+        grow(scratch, scratch_recs, size_t(n_records), 4096);
+        grow(scratch2, scratch2_recs, size_t(n_subs), 1024);
+        if (size_t(n_subs + n_groups) > n_tickets) {
             CK(cudaDeviceSynchronize());
             cudaFree(tickets);
             tickets = nullptr;
             n_tickets = 0;
-            const size_t nt = std::max<size_t>(size_t(n_groups) * 2, 1024);
+            const size_t nt = std::max<size_t>(size_t(n_subs + n_groups) * 2, 4096);
             CK(cudaMalloc(&tickets, nt * sizeof(int)));
             CK(cudaMemset(tickets, 0, nt * sizeof(int)));
             n_tickets = nt;
@@ -239,9 +250,9 @@ struct flint_attn {
             for (int j = 0; j < i; j++)
                 if (seqs[j] == seqs[i]) throw std::runtime_error("a sequence appears twice in one decode batch");
         }
-        int n_groups = 0, n_records = 0;
-        plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records);
-        ensure_scratch(n_records, n_groups);
+        int n_groups = 0, n_records = 0, n_subs = 0;
+        plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records, n_subs);
+        ensure_scratch(n_records, n_subs, n_groups);
         DecParams dp{};
         dp.items = upload_items(st);
         dp.qkv = qkv;
@@ -249,7 +260,8 @@ struct flint_attn {
         dp.partial_out = partial_out;
         dp.q_norm = L.q_norm; dp.k_norm = L.k_norm; dp.sinks = L.sinks; dp.inv_freq = inv_freq;
         dp.k_cache = L.k; dp.v_cache = L.v;
-        dp.scratch = scratch; dp.tickets = tickets;
+        dp.scratch = scratch; dp.scratch2 = scratch2;
+        dp.tickets = tickets; dp.tickets2 = tickets + n_subs;
         dp.seq_stride = (long long)kNHeadKv * L.n_slots * kHeadDim;
         dp.n_slots = L.n_slots;
         dp.slot_mask = L.is_swa ? uint32_t(kSwaRing - 1) : 0xFFFFFFFFu;
@@ -300,7 +312,7 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
         a->kv_rank = cfg->kv_rank;
         a->kv_ranks = ranks;
         a->sm_count = prop.multiProcessorCount;
-        a->target_items = a->sm_count * 2 * 4;
+        a->target_items = a->sm_count * 2;
         a->pos.assign(cfg->max_seqs, 0);
         CK(cudaStreamCreateWithFlags(&a->stream, cudaStreamNonBlocking));
         for (int i = 0; i < kRing; i++) CK(cudaEventCreateWithFlags(&a->ring_ev[i], cudaEventDisableTiming));
@@ -573,8 +585,8 @@ void *flint_attn_kv_dev(flint_attn *a, int32_t layer, int32_t which) {
 int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, int32_t kv_lo, int32_t kv_hi,
                                int32_t target_items, int32_t *out, int32_t cap) {
     std::vector<DecItem> items;
-    int n_groups = 0, n_records = 0;
-    plan_decode(n, nullptr, pos, is_swa != 0, kv_lo, kv_hi, target_items, items, n_groups, n_records);
+    int n_groups = 0, n_records = 0, n_subs = 0;
+    plan_decode(n, nullptr, pos, is_swa != 0, kv_lo, kv_hi, target_items, items, n_groups, n_records, n_subs);
     if (int(items.size()) > cap) return -1;
     for (size_t i = 0; i < items.size(); i++) {
         const DecItem &it = items[i];

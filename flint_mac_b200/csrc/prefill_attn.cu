@@ -35,15 +35,13 @@ constexpr int kHist = kNSwa - 1;      // 512 keys of history a sliding-window qu
 
 constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB, two 64-dim halves of [128 rows][128 B]
 constexpr int kKBytes = kBN * kHeadDim * 2;   // 16 KiB, two halves of [64 keys][128 B]
-constexpr int kPBytes = kBM * kBN * 2;        // 16 KiB, [128 rows][64 keys]
 constexpr int kOffQ = 0;
 constexpr int kOffK = kOffQ + kQBytes;
 constexpr int kOffV = kOffK + kStages * kKBytes;
-constexpr int kOffP = kOffV + kStages * kKBytes;
-constexpr int kOffBar = kOffP + kPBytes;
+constexpr int kOffBar = kOffV + kStages * kKBytes;
 constexpr int kOutBlockBytes = kQPos * kGqa * 128;  // one 128-byte-wide column block of the output tile
 static_assert(4 * kOutBlockBytes <= kQBytes + kStages * kKBytes, "the output tile reuses the Q and K buffers");
-constexpr int kSmemBytes = kOffBar + 128;  // 114816 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
+constexpr int kSmemBytes = kOffBar + 128;  // 98432 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
 
 #ifdef FLINT_PF_TRACE
 #define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 100 && blockIdx.y == 0) a.trace[(slot)] = clock64(); } while (0)
@@ -197,7 +195,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
         if (threadIdx.x == 0) atomicExch(a.error_flag, 2);
         return;
     }
-    const uint32_t sQ = base + kOffQ, sK = base + kOffK, sV = base + kOffV, sP = base + kOffP;
+    const uint32_t sQ = base + kOffQ, sK = base + kOffK, sV = base + kOffV;
     auto bar = [&](int i) { return base + kOffBar + 8u * uint32_t(i); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
 
@@ -242,7 +240,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                 tc5::tma_load_3d(sV + st * kKBytes + kKBytes / 2, &tm_v, bar(kBarVFull + st), 64, row, kvh);
             };
             constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
-            const uint32_t q_lo = tc5::desc_lo(sQ, 16), k_lo = tc5::desc_lo(sK, 16), p_lo = tc5::desc_lo(sP, 16);
+            const uint32_t q_lo = tc5::desc_lo(sQ, 16), k_lo = tc5::desc_lo(sK, 16);
             const uint32_t v_lo = tc5::desc_lo(sV, kKBytes / 2);
             auto issue_qk = [&](int kt) {
                 const int st = kt & 1;
@@ -301,8 +299,8 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                     const uint32_t vst = v_lo + uint32_t(st) * (kKBytes >> 4);
 #pragma unroll
                     for (int ks = 0; ks < kBN / 16; ks++)
-                        tc5::mma_f16_ss_lohi(tmem + kColO, p_lo + ks * 2, vst + ks * (2048 >> 4), kDescHi, kIdescPV,
-                                             (kt > 0 || ks > 0));
+                        tc5::mma_f16_ts_lohi(tmem + kColO, tmem + kColS + st * kBN + ks * 8, vst + ks * (2048 >> 4), kDescHi,
+                                             kIdescPV, (kt > 0 || ks > 0));
                 }
                 tc5::mma_commit(bar(kBarPvDone));
                 PF_TRACE(1000 + kt * 8 + 6);
@@ -382,36 +380,34 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                 l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
             if (tid == 0) PF_TRACE(kt * 8 + 3);
-            if (kt >= 1) {
-                // O and the P buffer belong to the tensor core until the P.V product of tile kt-1 has completed
+            if (kt >= 1 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // rare: O belongs to the tensor core until the P.V product of tile kt-1 has completed
                 ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (kt - 1) & 1));
                 if (!ok) break;
                 tc5::fence_after_sync();
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                    for (int cb = 0; cb < kHeadDim; cb += 32) {
-                        uint32_t r[32];
-                        tc5::tmem_ld32(lane_base + kColO + cb, r);
-                        tc5::tmem_wait_ld();
+                for (int cb = 0; cb < kHeadDim; cb += 32) {
+                    uint32_t r[32];
+                    tc5::tmem_ld32(lane_base + kColO + cb, r);
+                    tc5::tmem_wait_ld();
 #pragma unroll
-                        for (int c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-                        tc5::tmem_st32(lane_base + kColO + cb, r);
-                    }
-                    tc5::tmem_wait_st();
+                    for (int c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+                    tc5::tmem_st32(lane_base + kColO + cb, r);
                 }
             }
             if (tid == 0) PF_TRACE(kt * 8 + 4);
-            unsigned char *prow = gen + kOffP + tid * (kBN * 2);
-#pragma unroll
-            for (int ch = 0; ch < kBN / 8; ch++)
-                *reinterpret_cast<uint4 *>(prow + ((ch ^ (tid & 7)) << 4)) =
-                    make_uint4(pw[4 * ch], pw[4 * ch + 1], pw[4 * ch + 2], pw[4 * ch + 3]);
-            tc5::fence_proxy_async();
+            // P (half, two keys per 32-bit column) replaces the first 32 columns of this tile's S in tensor memory
+            // and is read from there as the A operand of P.V: no shared-memory round trip.
+            tc5::tmem_st32(lane_base + kColS + st * kBN, pw);
+            tc5::tmem_wait_st();
             tc5::fence_before_sync();
             tc5::mbar_arrive(bar(kBarPReady));
             if (tid == 0) PF_TRACE(kt * 8 + 5);
         }
         if (tid == 0) PF_TRACE(900);
+        // A parity wait is only meaningful for a waiter that knows the previous phase is over.  The scores of the last
+        // tile being ready proves P.V of tile n-3 done (it was issued before them), so wait for n-2, then for n-1.
+        if (ok && n_tiles >= 2) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (n_tiles - 2) & 1));
         if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (n_tiles - 1) & 1));
         if (ok) {
             // O / l (prefill.metal:255-265) goes out through shared memory: each thread drops its row into a

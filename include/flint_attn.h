@@ -140,7 +140,7 @@ int32_t flint_attn_set_pos(flint_attn *a, int32_t seq, int32_t pos);
  * src/engine.mm:742-743, is tuned for 32 splits on an M5).  Returns the item count, or -1 if cap is too small. */
 int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, int32_t kv_lo, int32_t kv_hi,
                                int32_t target_items, int32_t *items, int32_t cap);
-/* Tuning knob: work items the planner aims for per launch (default: 4 waves of 2 CTAs on every SM). */
+/* Tuning knob: work items the planner aims for per launch (default: one wave of 2 CTAs on every SM). */
 int32_t flint_attn_set_target_items(flint_attn *a, int32_t target_items);
 /* Number of kernel launches this handle has enqueued so far. */
 int64_t flint_attn_launch_count(const flint_attn *a);
@@ -163,7 +163,7 @@ double flint_attn_kernel_ms(flint_attn *a, int64_t *n_timed);
  * caches of the n sequences, half [n][4][n_slots][128] (row i of the batch uses cache i; n_slots = 1024 on a
  * sliding-window layer, the context length otherwise), q_norm/k_norm [128] and sinks [32] in fp32.  pos is a
  * HOST array of the n token positions.  What the kernel needs beyond that (work list, split-K partial records,
- * arrival counters, RoPE table) sits in one fixed array inside the library image, about 8.4 MiB on every GPU that
+ * arrival counters, RoPE table) sits in one fixed array inside the library image, about 10 MiB on every GPU that
  * loads the library, held until the process exits.  Limits: n <= FLINT_ATTN_NOALLOC_MAX_TOKENS and a split-K work
  * list of at most FLINT_ATTN_NOALLOC_MAX_ITEMS items; beyond either the call fails with a message and does nothing.
  *
