@@ -24,33 +24,38 @@ namespace flint {
 namespace {
 
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kQPos = 16;             // query positions per CTA
-constexpr int kBM = kQPos * kGqa;     // 128 query rows
-constexpr int kBN = 64;               // keys per tile
-constexpr int kStages = 2;
-constexpr int kTmemCols = 256;        // S (double-buffered): columns [0, 128), O: columns [128, 256)
-constexpr int kColS = 0, kColO = 128;
-constexpr int kThreadsAttn = kBM + 32; // 4 softmax warps + 1 issuing warp
-constexpr int kHist = kNSwa - 1;      // 512 keys of history a sliding-window query can see
+constexpr int kQPos = 16;              // query positions per 128-row Q tile (x 8 heads of the GQA group)
+constexpr int kBM = kQPos * kGqa;      // 128 query rows per Q tile
+constexpr int kQTiles = 2;             // Q tiles per CTA: they share every K/V tile and take turns on the tensor core
+constexpr int kCtaPos = kQPos * kQTiles;  // 32 query positions per CTA
+constexpr int kBN = 128;               // keys per tile: an MMA narrower than N = 128 runs at half rate
+constexpr int kSlots = 4;              // ring of 32 KiB tile slots, used alternately for K and V tiles
+constexpr int kHist = kNSwa - 1;       // 512 keys of history a sliding-window query can see
+// Tensor memory (all 512 columns): scores S per Q tile (P, as halves, is written over the first half of S) and the
+// output accumulators.
+constexpr int kTmemCols = 512;
+constexpr int kColS = 0;               // + 128 * tile
+constexpr int kColO = 256;             // + 128 * tile
+constexpr int kThreadsAttn = (kQTiles * 4 + 2) * 32;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
 
-constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB, two 64-dim halves of [128 rows][128 B]
-constexpr int kKBytes = kBN * kHeadDim * 2;   // 16 KiB, two halves of [64 keys][128 B]
+constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB per Q tile: two 64-dim halves of [128 rows][128 B]
+constexpr int kTileBytes = kBN * kHeadDim * 2;  // 32 KiB per K or V tile: two 64-dim halves of [128 keys][128 B]
 constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kQBytes;
-constexpr int kOffV = kOffK + kStages * kKBytes;
-constexpr int kOffBar = kOffV + kStages * kKBytes;
-constexpr int kOutBlockBytes = kQPos * kGqa * 128;  // one 128-byte-wide column block of the output tile
-static_assert(4 * kOutBlockBytes <= kQBytes + kStages * kKBytes, "the output tile reuses the Q and K buffers");
-constexpr int kSmemBytes = kOffBar + 128;  // 98432 B: two CTAs fit on one SM (and 2 x 256 tensor-memory columns)
+constexpr int kOffKV = kOffQ + kQTiles * kQBytes;
+constexpr int kOffBar = kOffKV + kSlots * kTileBytes;
+constexpr int kOutBlockBytes = kQPos * kGqa * 128;  // one 128-byte-wide column block of one Q tile's output
+static_assert(kQTiles * 4 * kOutBlockBytes <= kSlots * kTileBytes, "the output tiles reuse the K/V slots");
+constexpr int kSmemBytes = kOffBar + 256;  // 196864 B: one CTA per SM
 
 #ifdef FLINT_PF_TRACE
-#define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 100 && blockIdx.y == 0) a.trace[(slot)] = clock64(); } while (0)
+#define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 60 && blockIdx.y == 0) a.trace[(slot)] = clock64(); } while (0)
 #else
 #define PF_TRACE(slot) do { } while (0)
 #endif
 
 struct PfArgs {
     long long *trace;  // debug timeline (only with FLINT_PF_TRACE)
+    const __half *q_st;  // [32][n_tok][128] normalised, rotated, pre-scaled queries
     void *out;
     const float *sinks;
     int *error_flag;
@@ -176,14 +181,24 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
     }
 }
 
-// Barriers (8 bytes each, at kOffBar): the issuing thread and the 128 softmax threads only ever talk through these.
-enum { kBarQ = 0, kBarKFull = 1, kBarVFull = 3, kBarSReady = 5, kBarPReady = 7, kBarPvDone = 8, kNumBars = 9 };
+// Barriers (8 bytes each, at kOffBar): the warps only ever talk through these.
+enum {
+    kBarSlotFull = 0,                       // [kSlots] TMA -> MMA warp: the K or V tile of the slot has landed
+    kBarSlotEmpty = kBarSlotFull + kSlots,  // [kSlots] tensor core -> TMA warp: every product reading the slot is done
+    kBarQFull = kBarSlotEmpty + kSlots,     // [2] TMA -> MMA warp: the Q tile is in shared memory
+    kBarSReady = kBarQFull + 2,             // [2] tensor core -> softmax warps: S = Q.K^T of the current tile
+    kBarPReady = kBarSReady + 2,            // [2] softmax warps -> MMA warp: P is in tensor memory, S consumed (128 arrivals)
+    kBarPvDone = kBarPReady + 2,            // [2] tensor core -> softmax warps: O += P.V of the current tile
+    kBarAllDone = kBarPvDone + 2,           // tensor core -> everyone: nothing reads shared memory any more
+    kNumBars = kBarAllDone + 1
+};
 
-// 160 threads: warps 0-3 own the 128 query rows (softmax, P, lazy rescale, epilogue); lane 0 of warp 4 issues every
-// TMA copy and every MMA.  Tile kt's S = Q.K^T is issued before the softmax of tile kt-1 has finished (S is double
-// buffered in tensor memory), so the tensor core works on the next scores while the CUDA cores exponentiate the
-// current ones; two such CTAs share an SM.
-__global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
+// One CTA per SM, 320 threads.  Warps 0-3 own Q tile 0 (16 positions x 8 heads = 128 rows, one row per thread),
+// warps 4-7 Q tile 1 (the next 16 positions); warp 8 streams Q, K and V tiles with TMA (K and V alternate through a
+// ring of four 32 KiB slots); warp 9 issues every tcgen05.mma.  The two Q tiles share each K/V tile and alternate on
+// the tensor core: while one tile's warps run the softmax of key tile kt, the tensor core does P.V and the next
+// Q.K^T of the other.  P.V takes P from tensor memory; every product is 128 wide (N = 128).
+__global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_v,
                                                                   const __grid_constant__ CUtensorMap tm_o,
@@ -195,21 +210,22 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
         if (threadIdx.x == 0) atomicExch(a.error_flag, 2);
         return;
     }
-    const uint32_t sQ = base + kOffQ, sK = base + kOffK, sV = base + kOffV;
     auto bar = [&](int i) { return base + kOffBar + 8u * uint32_t(i); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int kvh = blockIdx.y;
-    const int t0 = blockIdx.x * kQPos;
+    const int t0 = blockIdx.x * kCtaPos;
     if (tid == 0) PF_TRACE(999);
     const int q_first = a.p0 + t0;
-    const int q_last = a.p0 + min(t0 + kQPos, a.n_tok) - 1;
+    const int q_last = a.p0 + min(t0 + kCtaPos, a.n_tok) - 1;
     const int klo = a.is_swa ? max(q_first - kHist, a.key_row0) : 0;
-    const int n_tiles = (q_last - klo) / kBN + 1;
+    const int n_keys = q_last - klo + 1;
+    const int n_tiles = (n_keys + kBN - 1) / kBN;
 
     if (tid == 0) {
-        for (int i = 0; i < kNumBars; i++) tc5::mbar_init(bar(i), i == kBarPReady ? kBM : 1);
+        for (int i = 0; i < kNumBars; i++)
+            tc5::mbar_init(bar(i), (i >= kBarPReady && i < kBarPReady + 2) ? kBM : 1);
         tc5::mbar_fence_init();
     }
     if (warp == 0) {
@@ -222,139 +238,166 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
-    if (warp == 4) {
-        // =========================================================== issuer: TMA + tcgen05.mma, one thread
+    if (warp == 8) {
+        // =========================================================== TMA producer
         if ((tid & 31) == 0) {
-            constexpr uint32_t kIdescQK = tc5::idesc_f16(kBM, kBN, 0, 0);       // A = Q (K-major), B = K (K-major)
-            constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);  // A = P (K-major), B = V (MN-major)
-            auto load_k = [&](int kt) {
-                const int st = kt & 1, row = klo + kt * kBN - a.key_row0;
-                tc5::mbar_expect_tx(bar(kBarKFull + st), kKBytes);
-                tc5::tma_load_3d(sK + st * kKBytes, &tm_k, bar(kBarKFull + st), 0, row, kvh);
-                tc5::tma_load_3d(sK + st * kKBytes + kKBytes / 2, &tm_k, bar(kBarKFull + st), 64, row, kvh);
-            };
-            auto load_v = [&](int kt) {
-                const int st = kt & 1, row = klo + kt * kBN - a.key_row0;
-                tc5::mbar_expect_tx(bar(kBarVFull + st), kKBytes);
-                tc5::tma_load_3d(sV + st * kKBytes, &tm_v, bar(kBarVFull + st), 0, row, kvh);
-                tc5::tma_load_3d(sV + st * kKBytes + kKBytes / 2, &tm_v, bar(kBarVFull + st), 64, row, kvh);
-            };
-            constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
-            const uint32_t q_lo = tc5::desc_lo(sQ, 16), k_lo = tc5::desc_lo(sK, 16);
-            const uint32_t v_lo = tc5::desc_lo(sV, kKBytes / 2);
-            auto issue_qk = [&](int kt) {
-                const int st = kt & 1;
-                const uint32_t kst = k_lo + uint32_t(st) * (kKBytes >> 4), d = tmem + kColS + st * kBN;
-#pragma unroll
-                for (int ks = 0; ks < kHeadDim / 16; ks++) {
-                    constexpr uint32_t kQHalf = (kQBytes / 2) >> 4, kKHalf = (kKBytes / 2) >> 4;
-                    tc5::mma_f16_ss_lohi(d, q_lo + (ks >> 2) * kQHalf + (ks & 3) * 2, kst + (ks >> 2) * kKHalf + (ks & 3) * 2,
-                                         kDescHi, kIdescQK, ks > 0);
-                }
-                tc5::mma_commit(bar(kBarSReady + st));
-            };
             tc5::prefetch_tmap(&tm_q);
             tc5::prefetch_tmap(&tm_k);
             tc5::prefetch_tmap(&tm_v);
-            tc5::mbar_expect_tx(bar(kBarQ), kQBytes);
-            tc5::tma_load_3d(sQ, &tm_q, bar(kBarQ), 0, t0, kvh * kGqa);
-            tc5::tma_load_3d(sQ + kQBytes / 2, &tm_q, bar(kBarQ), 64, t0, kvh * kGqa);
-            load_k(0);
-            if (n_tiles > 1) load_k(1);
-            load_v(0);
-            if (n_tiles > 1) load_v(1);
-            ok = wait_bar(bar(kBarQ), 0) && wait_bar(bar(kBarKFull), 0);
-            if (ok) issue_qk(0);
+            auto load_tile = [&](const CUtensorMap *map, int kt, int g) {  // g-th tile through the ring
+                const int slot = g % kSlots;
+                if (g >= kSlots && !wait_bar(bar(kBarSlotEmpty + slot), ((g / kSlots) - 1) & 1)) return false;
+                const uint32_t dst = base + kOffKV + slot * kTileBytes, full = bar(kBarSlotFull + slot);
+                const int row = klo + kt * kBN - a.key_row0;
+                tc5::mbar_expect_tx(full, kTileBytes);
+                tc5::tma_load_3d(dst, map, full, 0, row, kvh);
+                tc5::tma_load_3d(dst + kTileBytes / 2, map, full, 64, row, kvh);
+                return true;
+            };
+            // order of need: Q0, K(0), Q1, V(0), K(1), V(1), ...
+            tc5::mbar_expect_tx(bar(kBarQFull), kQBytes);
+            tc5::tma_load_3d(base + kOffQ, &tm_q, bar(kBarQFull), 0, t0, kvh * kGqa);
+            tc5::tma_load_3d(base + kOffQ + kQBytes / 2, &tm_q, bar(kBarQFull), 64, t0, kvh * kGqa);
+            ok = load_tile(&tm_k, 0, 0);
+            tc5::mbar_expect_tx(bar(kBarQFull + 1), kQBytes);
+            tc5::tma_load_3d(base + kOffQ + kQBytes, &tm_q, bar(kBarQFull + 1), 0, t0 + kQPos, kvh * kGqa);
+            tc5::tma_load_3d(base + kOffQ + kQBytes + kQBytes / 2, &tm_q, bar(kBarQFull + 1), 64, t0 + kQPos, kvh * kGqa);
             for (int kt = 0; kt < n_tiles && ok; kt++) {
-                const int st = kt & 1;
-                PF_TRACE(1000 + kt * 8 + 0);
-                if (kt + 1 < n_tiles) {
-                    // S[(kt+1)&1] was drained by the softmax of tile kt-1 (its P-ready arrival was waited for below)
-                    ok = wait_bar(bar(kBarKFull + (st ^ 1)), ((kt + 1) >> 1) & 1);
-                    if (!ok) break;
-                    issue_qk(kt + 1);
-                }
-                PF_TRACE(1000 + kt * 8 + 1);
-                if (kt >= 1 && kt + 1 < n_tiles) {
-                    // V stage of tile kt-1 is free once its P.V product has completed
-                    ok = wait_bar(bar(kBarPvDone), (kt - 1) & 1);
-                    if (!ok) break;
-                    load_v(kt + 1);
-                }
-                PF_TRACE(1000 + kt * 8 + 2);
-                if (kt + 2 < n_tiles) {
-                    // K stage of tile kt is free once Q.K^T of tile kt has completed
-                    ok = wait_bar(bar(kBarSReady + st), (kt >> 1) & 1);
-                    if (!ok) break;
-                    load_k(kt + 2);
-                }
-                PF_TRACE(1000 + kt * 8 + 3);
-                ok = wait_bar(bar(kBarPReady), kt & 1);
-                PF_TRACE(1000 + kt * 8 + 4);
-                ok = ok && wait_bar(bar(kBarVFull + st), (kt >> 1) & 1);
-                if (!ok) break;
-                PF_TRACE(1000 + kt * 8 + 5);
-                tc5::fence_after_sync();
-                {
-                    const uint32_t vst = v_lo + uint32_t(st) * (kKBytes >> 4);
-#pragma unroll
-                    for (int ks = 0; ks < kBN / 16; ks++)
-                        tc5::mma_f16_ts_lohi(tmem + kColO, tmem + kColS + st * kBN + ks * 8, vst + ks * (2048 >> 4), kDescHi,
-                                             kIdescPV, (kt > 0 || ks > 0));
-                }
-                tc5::mma_commit(bar(kBarPvDone));
-                PF_TRACE(1000 + kt * 8 + 6);
+                ok = load_tile(&tm_v, kt, 2 * kt + 1);
+                if (ok && kt + 1 < n_tiles) ok = load_tile(&tm_k, kt + 1, 2 * kt + 2);
             }
             if (!ok) atomicExch(a.error_flag, 1);
         }
+    } else if (warp == 9) {
+        // =========================================================== MMA issuer (warp-uniform code, one lane issues)
+        const uint32_t leader = (tid & 31) == 0;
+        constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
+        constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);  // A = P (tensor memory), B = V (MN-major)
+        const uint32_t q_lo = tc5::desc_lo(base + kOffQ, 16);
+        const uint32_t k_lo = tc5::desc_lo(base + kOffKV, 16);               // K tile: K-major, two 64-dim halves
+        const uint32_t v_lo = tc5::desc_lo(base + kOffKV, kTileBytes / 2);   // V tile: MN-major, LBO = the other 64 dims
+        // keys of a tile that any query of the CTA can see, rounded up to the MMA's N granularity
+        auto tile_n = [&](int kt) { return min(kBN, (n_keys - kt * kBN + 15) & ~15); };
+        auto issue_qk = [&](int w, int kt) {
+            const uint32_t kst = k_lo + uint32_t((2 * kt) % kSlots) * (kTileBytes >> 4);
+            const uint32_t idesc = tc5::idesc_f16(kBM, tile_n(kt), 0, 0);  // A = Q (K-major), B = K (K-major)
+#pragma unroll
+            for (int ks = 0; ks < kHeadDim / 16; ks++) {
+                const uint32_t off = (ks >> 2) * ((kTileBytes / 2) >> 4) + (ks & 3) * 2;  // Q and K halves are both 16 KiB
+                tc5::mma_f16_ss_lohi_w(tmem + kColS + w * kBN, q_lo + w * (kQBytes >> 4) + off, kst + off, kDescHi, idesc,
+                                       ks > 0, leader);
+            }
+            tc5::mma_commit_w(bar(kBarSReady + w), leader);
+        };
+        auto issue_pv = [&](int w, int kt) {
+            const uint32_t vst = v_lo + uint32_t((2 * kt + 1) % kSlots) * (kTileBytes >> 4);
+            const int n_steps = tile_n(kt) / 16;
+#pragma unroll 1
+            for (int ks = 0; ks < n_steps; ks++)
+                tc5::mma_f16_ts_lohi_w(tmem + kColO + w * kHeadDim, tmem + kColS + w * kBN + ks * 8, vst + ks * (2048 >> 4),
+                                       kDescHi, kIdescPV, (kt > 0 || ks > 0), leader);
+            tc5::mma_commit_w(bar(kBarPvDone + w), leader);
+        };
+        ok = wait_bar(bar(kBarQFull), 0) && wait_bar(bar(kBarSlotFull), 0);
+        if (ok) {
+            tc5::fence_after_sync();
+            issue_qk(0, 0);
+            ok = wait_bar(bar(kBarQFull + 1), 0);
+        }
+        if (ok) {
+            issue_qk(1, 0);
+            tc5::mma_commit_w(bar(kBarSlotEmpty), leader);  // K(0) has been read by both Q tiles once these complete
+        }
+        for (int kt = 0; kt < n_tiles && ok; kt++) {
+            const bool more = kt + 1 < n_tiles;
+            const int vslot = (2 * kt + 1) % kSlots, kslot = (2 * kt + 2) % kSlots;
+#pragma unroll
+            for (int w = 0; w < kQTiles; w++) {
+                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w);
+                ok = wait_bar(bar(kBarPReady + w), kt & 1);
+                if (ok && w == 0) ok = wait_bar(bar(kBarSlotFull + vslot), ((2 * kt + 1) / kSlots) & 1);
+                if (!ok) break;
+                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w + 1);
+                tc5::fence_after_sync();
+                issue_pv(w, kt);
+                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w + 2);
+                if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + vslot), leader);
+                if (more) {
+                    // S of this Q tile is free again: its P is consumed by the product just issued, in order
+                    if (w == 0) {
+                        ok = wait_bar(bar(kBarSlotFull + kslot), ((2 * kt + 2) / kSlots) & 1);
+                        if (!ok) break;
+                    }
+                    issue_qk(w, kt + 1);
+                    if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + kslot), leader);
+                }
+                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w + 3);
+            }
+        }
+        if (ok) tc5::mma_commit_w(bar(kBarAllDone), leader);
+        else if (leader) atomicExch(a.error_flag, 1);
     } else {
         // =========================================================== softmax warps: one query row per thread
-        const int hl = tid >> 4, qi = tid & 15;  // row = head-in-group * 16 + position-in-block (the TMA box order)
-        const int qpos = q_first + qi;
+        const int w = warp >> 2;                   // Q tile of this warp
+        const int r = tid & (kBM - 1);             // row in the tile = head-in-group * 16 + position-in-tile
+        const int hl = r >> 4, qi = r & 15;
+        const int qpos = q_first + w * kQPos + qi;
+        const int qt_first = q_first + w * kQPos;  // first / last position of this Q tile
+        const int qt_last = min(qt_first + kQPos - 1, q_last);
         const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
-        float m = sink2, l = 1.0f;  // prefill.metal:162
-        const uint32_t lane_base = tmem + (uint32_t(warp * 32) << 16);
+        const uint32_t lane_base = tmem + (uint32_t((warp & 3) * 32) << 16);
+        const uint32_t colS = lane_base + kColS + w * kBN, colO = lane_base + kColO + w * kHeadDim;
 
+        float m = sink2, l = 1.0f;  // prefill.metal:162
         for (int kt = 0; kt < n_tiles && ok; kt++) {
-            const int st = kt & 1;
-            if (tid == 0) PF_TRACE(kt * 8 + 0);
-            ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + st), (kt >> 1) & 1));  // warp-uniform for tcgen05.ld
+            if (r == 0) PF_TRACE(w * 400 + kt * 8 + 0);
+            ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + w), kt & 1));  // warp-uniform for tcgen05.ld
             if (!ok) break;
-            if (tid == 0) PF_TRACE(kt * 8 + 1);
+            if (r == 0) PF_TRACE(w * 400 + kt * 8 + 1);
             tc5::fence_after_sync();
-            float s[kBN];
-            {
-                uint32_t r0[32], r1[32];
-                tc5::tmem_ld32(lane_base + kColS + st * kBN, r0);
-                tc5::tmem_ld32(lane_base + kColS + st * kBN + 32, r1);
-                tc5::tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    s[c] = __uint_as_float(r0[c]);
-                    s[c + 32] = __uint_as_float(r1[c]);
-                }
-            }
-            if (tid == 0) PF_TRACE(kt * 8 + 2);
             const int kbase = klo + kt * kBN;
-            // interior tiles of the band are visible to all 16 positions of the block: no per-element mask
-            const bool need_mask = kbase + kBN - 1 > q_first || (a.is_swa && kbase < q_last - kHist);
+            const int n_cols = min(kBN, (n_keys - kt * kBN + 15) & ~15);  // columns the MMA wrote (same as the issuer)
+            const int n_chunks = (n_cols + 31) >> 5;
+            // visible columns of this row form one range [c_lo, c_hi] (prefill.metal:212)
+            const int c_hi = qpos - kbase;
+            const int c_lo = a.is_swa ? qpos - kHist - kbase : -(1 << 30);
+            // Per 32-column chunk, for the whole Q tile: 0 = every row sees every key (no per-element mask),
+            // 1 = mixed, 2 = no row sees any key.  Only the two ends of the band are mixed.
+            auto chunk_kind = [&](int ch) {
+                const int key_lo = kbase + ch * 32, key_hi = key_lo + 31;
+                if (key_lo > qt_last || (a.is_swa && key_hi < qt_first - kHist)) return 2;
+                if (key_hi <= qt_first && (!a.is_swa || key_lo >= qt_last - kHist)) return 0;
+                return 1;
+            };
+
+            // the whole row of S in registers (one pass over tensor memory), masked where needed
+            uint32_t sr[kBN];
             float mx = -INFINITY;
-            if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < kBN; c++) {
-                    const int kpos = kbase + c;
-                    const bool vis = kpos <= qpos && (!a.is_swa || qpos - kpos <= kHist);  // prefill.metal:212
-                    s[c] = vis ? s[c] : -INFINITY;
-                    mx = fmaxf(mx, s[c]);
-                }
-            } else {
-                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains instead of one
+            for (int ch = 0; ch < kBN / 32; ch++) {
+                if (ch < n_chunks) {
+                    uint32_t t32[32];
+                    tc5::tmem_ld32(colS + ch * 32, t32);
+                    tc5::tmem_wait_ld();
+                    const int kind = chunk_kind(ch);
+                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                    if (kind == 0) {
 #pragma unroll
-                for (int c = 0; c < kBN; c += 4) {
-                    m4[0] = fmaxf(m4[0], s[c]); m4[1] = fmaxf(m4[1], s[c + 1]);
-                    m4[2] = fmaxf(m4[2], s[c + 2]); m4[3] = fmaxf(m4[3], s[c + 3]);
+                        for (int c = 0; c < 32; c++) {
+                            sr[ch * 32 + c] = t32[c];
+                            m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(t32[c]));
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; c++) {
+                            const int col = ch * 32 + c;
+                            const uint32_t v = (kind == 1 && col >= c_lo && col <= c_hi) ? t32[c] : 0xff800000u;  // -inf
+                            sr[ch * 32 + c] = v;
+                            m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(v));
+                        }
+                    }
+                    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
                 }
-                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             // lazy rescale: keep the old reference maximum unless the row maximum outgrew it by more than 2^8
             float corr = 1.0f;
@@ -366,98 +409,98 @@ __global__ void __launch_bounds__(kThreadsAttn, 2) k_prefill_attn(const __grid_c
                 m = mx;
                 l *= corr;
             }
-            uint32_t pw[kBN / 2];
-            {
-                float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int c = 0; c < kBN; c += 4) {
-                    const float p0 = fast_exp2(s[c] - m), p1 = fast_exp2(s[c + 1] - m);
-                    const float p2 = fast_exp2(s[c + 2] - m), p3 = fast_exp2(s[c + 3] - m);
-                    sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
-                    pw[c >> 1] = pack_half2(p0, p1);
-                    pw[(c >> 1) + 1] = pack_half2(p2, p3);
-                }
-                l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            }
-            if (tid == 0) PF_TRACE(kt * 8 + 3);
             if (kt >= 1 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // rare: O belongs to the tensor core until the P.V product of tile kt-1 has completed
-                ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (kt - 1) & 1));
-                if (!ok) break;
-                tc5::fence_after_sync();
-#pragma unroll
+                // rare.  These scores were computed after P.V of the previous tile (same issue order), so O is idle.
+#pragma unroll 1
                 for (int cb = 0; cb < kHeadDim; cb += 32) {
-                    uint32_t r[32];
-                    tc5::tmem_ld32(lane_base + kColO + cb, r);
+                    uint32_t rr[32];
+                    tc5::tmem_ld32(colO + cb, rr);
                     tc5::tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < 32; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-                    tc5::tmem_st32(lane_base + kColO + cb, r);
+                    for (int c = 0; c < 32; c++) rr[c] = __float_as_uint(__uint_as_float(rr[c]) * corr);
+                    tc5::tmem_st32(colO + cb, rr);
                 }
             }
-            if (tid == 0) PF_TRACE(kt * 8 + 4);
-            // P (half, two keys per 32-bit column) replaces the first 32 columns of this tile's S in tensor memory
-            // and is read from there as the A operand of P.V: no shared-memory round trip.
-            tc5::tmem_st32(lane_base + kColS + st * kBN, pw);
+            // probabilities: P (half, two keys per 32-bit column) goes over the first half of S in tensor memory
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ch = 0; ch < kBN / 32; ch++) {
+                if (ch < n_chunks) {
+                    uint32_t pw[16];
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float p0 = fast_exp2(__uint_as_float(sr[ch * 32 + c]) - m);
+                        const float p1 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 1]) - m);
+                        const float p2 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 2]) - m);
+                        const float p3 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 3]) - m);
+                        sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
+                        pw[c >> 1] = pack_half2(p0, p1);
+                        pw[(c >> 1) + 1] = pack_half2(p2, p3);
+                    }
+                    tc5::tmem_st16(colS + ch * 16, pw);
+                }
+            }
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tc5::tmem_wait_st();
             tc5::fence_before_sync();
-            tc5::mbar_arrive(bar(kBarPReady));
-            if (tid == 0) PF_TRACE(kt * 8 + 5);
+            tc5::mbar_arrive(bar(kBarPReady + w));
+            if (r == 0) PF_TRACE(w * 400 + kt * 8 + 2);
         }
-        if (tid == 0) PF_TRACE(900);
-        // A parity wait is only meaningful for a waiter that knows the previous phase is over.  The scores of the last
-        // tile being ready proves P.V of tile n-3 done (it was issued before them), so wait for n-2, then for n-1.
-        if (ok && n_tiles >= 2) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (n_tiles - 2) & 1));
-        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone), (n_tiles - 1) & 1));
+        if (r == 0) PF_TRACE(900 + w);
+        // The scores of the last tile prove P.V of tile n-2 done, so a parity wait for tile n-1 is well defined.
+        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone + w), (n_tiles - 1) & 1));
+        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarAllDone), 0));  // the K/V slots become the output tiles
         if (ok) {
             // O / l (prefill.metal:255-265) goes out through shared memory: each thread drops its row into a
-            // [16 positions][8 heads][128 B] swizzled tile per 128-byte column block (the Q and K buffers are idle by
-            // now), then one thread hands the tiles to TMA, which writes full lines and clips rows past the prompt.
+            // [8 heads][16 positions][128 B] swizzled tile per 128-byte column block, then one thread per Q tile hands
+            // the tiles to TMA, which writes full lines and clips rows past the prompt.
             tc5::fence_after_sync();
             const float inv_l = 1.0f / l;
-            const int R = qi * kGqa + hl;
-            unsigned char *stg = gen + kOffQ + R * 128;
+            const int R = r;  // tile rows ordered [8 heads][16 positions], the order of the output tensor map's box
+            const uint32_t stage_off = kOffKV + w * 4 * kOutBlockBytes;
+            unsigned char *stg = gen + stage_off + R * 128;
             const int sw = R & 7;
 #pragma unroll
             for (int cb = 0; cb < kHeadDim; cb += 32) {
-                uint32_t r[32];
-                tc5::tmem_ld32(lane_base + kColO + cb, r);
+                uint32_t rr[32];
+                tc5::tmem_ld32(colO + cb, rr);
                 tc5::tmem_wait_ld();
                 if (a.out_dtype == kDtypeF32) {
                     unsigned char *blk = stg + (cb / 32) * kOutBlockBytes;
 #pragma unroll
                     for (int c = 0; c < 8; c++)
                         *reinterpret_cast<float4 *>(blk + ((c ^ sw) << 4)) =
-                            make_float4(__uint_as_float(r[4 * c]) * inv_l, __uint_as_float(r[4 * c + 1]) * inv_l,
-                                        __uint_as_float(r[4 * c + 2]) * inv_l, __uint_as_float(r[4 * c + 3]) * inv_l);
+                            make_float4(__uint_as_float(rr[4 * c]) * inv_l, __uint_as_float(rr[4 * c + 1]) * inv_l,
+                                        __uint_as_float(rr[4 * c + 2]) * inv_l, __uint_as_float(rr[4 * c + 3]) * inv_l);
                 } else {
                     unsigned char *blk = stg + (cb / 64) * kOutBlockBytes;
 #pragma unroll
                     for (int c = 0; c < 4; c++) {
-                        uint32_t w[4];
+                        uint32_t wd[4];
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[8 * c + 2 * j]) * inv_l,
-                                                                           __uint_as_float(r[8 * c + 2 * j + 1]) * inv_l);
-                            w[j] = *reinterpret_cast<const uint32_t *>(&b);
+                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(rr[8 * c + 2 * j]) * inv_l,
+                                                                           __uint_as_float(rr[8 * c + 2 * j + 1]) * inv_l);
+                            wd[j] = *reinterpret_cast<const uint32_t *>(&b);
                         }
-                        *reinterpret_cast<uint4 *>(blk + ((((cb & 32) >> 3) + c) ^ sw) * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4 *>(blk + ((((cb & 32) >> 3) + c) ^ sw) * 16) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
                     }
                 }
             }
             tc5::fence_proxy_async();
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four softmax warps only
-            if (tid == 0) {
+            if (w == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four warps of this Q tile only
+            else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+            if (r == 0 && t0 + w * kQPos < a.n_tok) {
                 const int n_blk = a.out_dtype == kDtypeF32 ? 4 : 2, x_step = a.out_dtype == kDtypeF32 ? 32 : 64;
                 for (int b = 0; b < n_blk; b++)
-                    tc5::tma_store_3d(&tm_o, sQ + b * kOutBlockBytes, b * x_step, kvh * kGqa, t0);
+                    tc5::tma_store_3d(&tm_o, base + stage_off + b * kOutBlockBytes, b * x_step, t0 + w * kQPos, kvh * kGqa);
                 tc5::tma_store_commit_and_wait_read();
             }
         } else if ((tid & 31) == 0) {
             atomicExch(a.error_flag, 1);  // a wait ran out: report, then leave through the normal teardown
         }
+        if (r == 0) PF_TRACE(910 + w);
     }
-    if (tid == 0) PF_TRACE(901);
     tc5::fence_before_sync();
     __syncthreads();
     if (warp == 0) tc5::tmem_dealloc(tmem, kTmemCols);
@@ -484,12 +527,13 @@ cudaError_t make_map(CUtensorMap *map, const void *base, int n_rows, int n_outer
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-// output [n_tok][32][128] (bf16 or f32) viewed as {128, 32, n_tok}; box = one 128-byte column block x 8 heads x 16 tokens
+// output [n_tok][32][128] (bf16 or f32) viewed as {128 dims, n_tok, 32 heads}; box = one 128-byte column block x 16
+// tokens x 8 heads, so that the shared-memory tile has the kernel's row order (head-major)
 cudaError_t make_out_map(CUtensorMap *map, void *base, int n_tok, int out_dtype) {
     const cuuint64_t es = out_dtype == kDtypeF32 ? 4 : 2;
-    const cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(kNHead), cuuint64_t(n_tok)};
-    const cuuint64_t strides[2] = {cuuint64_t(kHeadDim) * es, cuuint64_t(kQDim) * es};
-    const cuuint32_t box[3] = {cuuint32_t(128 / es), cuuint32_t(kGqa), cuuint32_t(kQPos)};
+    const cuuint64_t dims[3] = {cuuint64_t(kHeadDim), cuuint64_t(n_tok), cuuint64_t(kNHead)};
+    const cuuint64_t strides[2] = {cuuint64_t(kQDim) * es, cuuint64_t(kHeadDim) * es};
+    const cuuint32_t box[3] = {cuuint32_t(128 / es), cuuint32_t(kQPos), cuuint32_t(kGqa)};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = g_encode(map, out_dtype == kDtypeF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
                                 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -582,10 +626,11 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
         g_trace_buf = trace_buf;
     }
 #endif
+    a.q_st = q_st;
     a.out = p.out; a.sinks = p.sinks; a.error_flag = err_flag; a.out_dtype = p.out_dtype;
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
-    const dim3 grid((T + kQPos - 1) / kQPos, kNHeadKv);
+    const dim3 grid((T + kCtaPos - 1) / kCtaPos, kNHeadKv);
     if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
     k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
     if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
