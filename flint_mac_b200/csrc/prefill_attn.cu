@@ -29,7 +29,7 @@ constexpr int kBM = kQPos * kGqa;      // 128 query rows per Q tile
 constexpr int kQTiles = 2;             // Q tiles per CTA: they share every K/V tile and take turns on the tensor core
 constexpr int kCtaPos = kQPos * kQTiles;  // 32 query positions per CTA
 constexpr int kBN = 128;               // keys per tile: an MMA narrower than N = 128 runs at half rate
-constexpr int kSlots = 4;              // ring of 32 KiB tile slots, used alternately for K and V tiles
+constexpr int kSlots = 3;              // ring of 32 KiB tile slots, used alternately for K and V tiles
 constexpr int kHist = kNSwa - 1;       // 512 keys of history a sliding-window query can see
 // Tensor memory (all 512 columns): scores S per Q tile (P, as halves, is written over the first half of S) and the
 // output accumulators.
@@ -42,13 +42,13 @@ constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB per Q tile: two 64-dim h
 constexpr int kTileBytes = kBN * kHeadDim * 2;  // 32 KiB per K or V tile: two 64-dim halves of [128 keys][128 B]
 constexpr int kOffQ = 0;
 constexpr int kOffKV = kOffQ + kQTiles * kQBytes;
-constexpr int kOffBar = kOffKV + kSlots * kTileBytes;
 constexpr int kOutBlockBytes = kQPos * kGqa * 128;  // one 128-byte-wide column block of one Q tile's output
-static_assert(kQTiles * 4 * kOutBlockBytes <= kSlots * kTileBytes, "the output tiles reuse the K/V slots");
-constexpr int kSmemBytes = kOffBar + 256;  // 196864 B: one CTA per SM
+constexpr int kOffStage = kOffKV + kSlots * kTileBytes;  // output staging: two column blocks per Q tile
+constexpr int kOffBar = kOffStage + kQTiles * 2 * kOutBlockBytes;
+constexpr int kSmemBytes = kOffBar + 256;  // 229632 B: one CTA per SM
 
 #ifdef FLINT_PF_TRACE
-#define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 60 && blockIdx.y == 0) a.trace[(slot)] = clock64(); } while (0)
+#define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 60) a.trace[(slot)] = clock64(); } while (0)
 #else
 #define PF_TRACE(slot) do { } while (0)
 #endif
@@ -181,23 +181,46 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
     }
 }
 
-// Barriers (8 bytes each, at kOffBar): the warps only ever talk through these.
+// Barriers (8 bytes each, at kOffBar): the warps only ever talk through these.  Every barrier completes one phase
+// per use, and each waiter counts its own uses, so the phase parities stay valid across the work units of a CTA.
 enum {
     kBarSlotFull = 0,                       // [kSlots] TMA -> MMA warp: the K or V tile of the slot has landed
     kBarSlotEmpty = kBarSlotFull + kSlots,  // [kSlots] tensor core -> TMA warp: every product reading the slot is done
-    kBarQFull = kBarSlotEmpty + kSlots,     // [2] TMA -> MMA warp: the Q tile is in shared memory
-    kBarSReady = kBarQFull + 2,             // [2] tensor core -> softmax warps: S = Q.K^T of the current tile
+    kBarQFull = kBarSlotEmpty + kSlots,     // [2] TMA -> MMA warp: the Q tile of the unit is in shared memory
+    kBarQEmpty = kBarQFull + 2,             // [2] tensor core -> TMA warp: the unit's last Q.K^T of this Q tile is done
+    kBarSReady = kBarQEmpty + 2,            // [2] tensor core -> softmax warps: S = Q.K^T of the current tile
     kBarPReady = kBarSReady + 2,            // [2] softmax warps -> MMA warp: P is in tensor memory, S consumed (128 arrivals)
     kBarPvDone = kBarPReady + 2,            // [2] tensor core -> softmax warps: O += P.V of the current tile
-    kBarAllDone = kBarPvDone + 2,           // tensor core -> everyone: nothing reads shared memory any more
-    kNumBars = kBarAllDone + 1
+    kBarOFree = kBarPvDone + 2,             // [2] softmax warps -> MMA warp: O of the finished unit has been read out (128)
+    kNumBars = kBarOFree + 2
 };
 
-// One CTA per SM, 320 threads.  Warps 0-3 own Q tile 0 (16 positions x 8 heads = 128 rows, one row per thread),
-// warps 4-7 Q tile 1 (the next 16 positions); warp 8 streams Q, K and V tiles with TMA (K and V alternate through a
-// ring of four 32 KiB slots); warp 9 issues every tcgen05.mma.  The two Q tiles share each K/V tile and alternate on
-// the tensor core: while one tile's warps run the softmax of key tile kt, the tensor core does P.V and the next
-// Q.K^T of the other.  P.V takes P from tensor memory; every product is 128 wide (N = 128).
+// A work unit: 32 consecutive query positions (two Q tiles of 16 positions x 8 heads) of one KV head.
+struct Unit {
+    int t0, kvh, q_first, q_last, klo, n_keys, n_tiles;
+};
+// Units are handed out longest first: late query blocks (full 544-key bands) before the first 16 blocks of the
+// prompt, whose bands are shorter, so that the CTAs that get one unit more than the others get short ones.
+__device__ __forceinline__ Unit unit_geom(const PfArgs &a, int u) {
+    Unit g;
+    const int n_qb = (a.n_tok + kCtaPos - 1) / kCtaPos;
+    g.t0 = (n_qb - 1 - u / kNHeadKv) * kCtaPos;
+    g.kvh = u % kNHeadKv;
+    g.q_first = a.p0 + g.t0;
+    g.q_last = a.p0 + min(g.t0 + kCtaPos, a.n_tok) - 1;
+    g.klo = a.is_swa ? max(g.q_first - kHist, a.key_row0) : 0;
+    g.n_keys = g.q_last - g.klo + 1;
+    g.n_tiles = (g.n_keys + kBN - 1) / kBN;
+    return g;
+}
+
+// Persistent: one CTA per SM, 320 threads, each CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ...
+// Warps 0-3 own Q tile 0 of the unit (128 rows, one row per thread), warps 4-7 Q tile 1; warp 8 streams Q, K and V
+// tiles with TMA (K and V alternate through a ring of three 32 KiB slots); warp 9 issues every tcgen05.mma.  The two
+// Q tiles share each K/V tile and alternate on the tensor core: while one tile's warps run the softmax of a key tile,
+// the tensor core does P.V and the next Q.K^T of the other -- across unit boundaries too, so the start-up of a unit
+// (Q load, first scores) and the drain of the previous one (O / l, TMA store) overlap.  P.V takes P from tensor
+// memory; every product is 128 wide (N = 128; narrower MMAs run at half rate).
 __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_v,
@@ -214,18 +237,14 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int kvh = blockIdx.y;
-    const int t0 = blockIdx.x * kCtaPos;
+    const int n_units = ((a.n_tok + kCtaPos - 1) / kCtaPos) * kNHeadKv;
     if (tid == 0) PF_TRACE(999);
-    const int q_first = a.p0 + t0;
-    const int q_last = a.p0 + min(t0 + kCtaPos, a.n_tok) - 1;
-    const int klo = a.is_swa ? max(q_first - kHist, a.key_row0) : 0;
-    const int n_keys = q_last - klo + 1;
-    const int n_tiles = (n_keys + kBN - 1) / kBN;
 
     if (tid == 0) {
-        for (int i = 0; i < kNumBars; i++)
-            tc5::mbar_init(bar(i), (i >= kBarPReady && i < kBarPReady + 2) ? kBM : 1);
+        for (int i = 0; i < kNumBars; i++) {
+            const bool many = (i >= kBarPReady && i < kBarPReady + 2) || (i >= kBarOFree && i < kBarOFree + 2);
+            tc5::mbar_init(bar(i), many ? kBM : 1);
+        }
         tc5::mbar_fence_init();
     }
     if (warp == 0) {
@@ -244,27 +263,35 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             tc5::prefetch_tmap(&tm_q);
             tc5::prefetch_tmap(&tm_k);
             tc5::prefetch_tmap(&tm_v);
-            auto load_tile = [&](const CUtensorMap *map, int kt, int g) {  // g-th tile through the ring
-                const int slot = g % kSlots;
-                if (g >= kSlots && !wait_bar(bar(kBarSlotEmpty + slot), ((g / kSlots) - 1) & 1)) return false;
+            int g = 0;  // tiles sent through the ring so far
+            auto load_tile = [&](const CUtensorMap *map, const Unit &un, int kt) {
+                const int slot = g % kSlots, use = g / kSlots;
+                g++;
+                if (use >= 1 && !wait_bar(bar(kBarSlotEmpty + slot), (use - 1) & 1)) return false;
                 const uint32_t dst = base + kOffKV + slot * kTileBytes, full = bar(kBarSlotFull + slot);
-                const int row = klo + kt * kBN - a.key_row0;
+                const int row = un.klo + kt * kBN - a.key_row0;
                 tc5::mbar_expect_tx(full, kTileBytes);
-                tc5::tma_load_3d(dst, map, full, 0, row, kvh);
-                tc5::tma_load_3d(dst + kTileBytes / 2, map, full, 64, row, kvh);
+                tc5::tma_load_3d(dst, map, full, 0, row, un.kvh);
+                tc5::tma_load_3d(dst + kTileBytes / 2, map, full, 64, row, un.kvh);
                 return true;
             };
-            // order of need: Q0, K(0), Q1, V(0), K(1), V(1), ...
-            tc5::mbar_expect_tx(bar(kBarQFull), kQBytes);
-            tc5::tma_load_3d(base + kOffQ, &tm_q, bar(kBarQFull), 0, t0, kvh * kGqa);
-            tc5::tma_load_3d(base + kOffQ + kQBytes / 2, &tm_q, bar(kBarQFull), 64, t0, kvh * kGqa);
-            ok = load_tile(&tm_k, 0, 0);
-            tc5::mbar_expect_tx(bar(kBarQFull + 1), kQBytes);
-            tc5::tma_load_3d(base + kOffQ + kQBytes, &tm_q, bar(kBarQFull + 1), 0, t0 + kQPos, kvh * kGqa);
-            tc5::tma_load_3d(base + kOffQ + kQBytes + kQBytes / 2, &tm_q, bar(kBarQFull + 1), 64, t0 + kQPos, kvh * kGqa);
-            for (int kt = 0; kt < n_tiles && ok; kt++) {
-                ok = load_tile(&tm_v, kt, 2 * kt + 1);
-                if (ok && kt + 1 < n_tiles) ok = load_tile(&tm_k, kt + 1, 2 * kt + 2);
+            auto load_q = [&](const Unit &un, int w, int i) {
+                if (i >= 1 && !wait_bar(bar(kBarQEmpty + w), (i - 1) & 1)) return false;
+                const uint32_t dst = base + kOffQ + w * kQBytes, full = bar(kBarQFull + w);
+                tc5::mbar_expect_tx(full, kQBytes);
+                tc5::tma_load_3d(dst, &tm_q, full, 0, un.t0 + w * kQPos, un.kvh * kGqa);
+                tc5::tma_load_3d(dst + kQBytes / 2, &tm_q, full, 64, un.t0 + w * kQPos, un.kvh * kGqa);
+                return true;
+            };
+            int i = 0;
+            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, i++) {
+                const Unit un = unit_geom(a, u);
+                // order of need: Q0, K(0), Q1, V(0), K(1), V(1), ...
+                ok = load_q(un, 0, i) && load_tile(&tm_k, un, 0) && load_q(un, 1, i);
+                for (int kt = 0; kt < un.n_tiles && ok; kt++) {
+                    ok = load_tile(&tm_v, un, kt);
+                    if (ok && kt + 1 < un.n_tiles) ok = load_tile(&tm_k, un, kt + 1);
+                }
             }
             if (!ok) atomicExch(a.error_flag, 1);
         }
@@ -276,11 +303,35 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         const uint32_t q_lo = tc5::desc_lo(base + kOffQ, 16);
         const uint32_t k_lo = tc5::desc_lo(base + kOffKV, 16);               // K tile: K-major, two 64-dim halves
         const uint32_t v_lo = tc5::desc_lo(base + kOffKV, kTileBytes / 2);   // V tile: MN-major, LBO = the other 64 dims
-        // keys of a tile that any query of the CTA can see, rounded up to the MMA's N granularity
-        auto tile_n = [&](int kt) { return min(kBN, (n_keys - kt * kBN + 15) & ~15); };
-        auto issue_qk = [&](int w, int kt) {
-            const uint32_t kst = k_lo + uint32_t((2 * kt) % kSlots) * (kTileBytes >> 4);
-            const uint32_t idesc = tc5::idesc_f16(kBM, tile_n(kt), 0, 0);  // A = Q (K-major), B = K (K-major)
+        // The key tiles of all units of this CTA form one stream; tile j of the stream has its K in ring use 2j and
+        // its V in ring use 2j + 1.  For each tile and Q tile w: P.V, then Q.K^T of the NEXT tile of the stream (S of w
+        // is free again: its P is consumed by the product just issued, in order), possibly of the next unit.
+        struct Cursor {
+            int u, i, kt, j;  // unit, index of the unit in this CTA, tile in the unit, tile in the stream
+            Unit un;
+        };
+        // keys of a tile that any query of the unit can see, rounded up to the MMA's N granularity
+        auto tile_n = [&](const Cursor &c) { return min(kBN, (c.un.n_keys - c.kt * kBN + 15) & ~15); };
+        auto advance = [&](Cursor &c) {  // returns false at the end of the stream
+            if (c.kt + 1 < c.un.n_tiles) {
+                c.kt++;
+            } else {
+                c.u += gridDim.x;
+                if (c.u >= n_units) return false;
+                c.i++;
+                c.kt = 0;
+                c.un = unit_geom(a, c.u);
+            }
+            c.j++;
+            return true;
+        };
+        auto issue_qk = [&](int w, const Cursor &c) {
+            const int g = 2 * c.j, slot = g % kSlots;
+            if (c.kt == 0 && !wait_bar(bar(kBarQFull + w), c.i & 1)) return false;
+            if (w == 0 && !wait_bar(bar(kBarSlotFull + slot), (g / kSlots) & 1)) return false;
+            tc5::fence_after_sync();
+            const uint32_t kst = k_lo + uint32_t(slot) * (kTileBytes >> 4);
+            const uint32_t idesc = tc5::idesc_f16(kBM, tile_n(c), 0, 0);  // A = Q (K-major), B = K (K-major)
 #pragma unroll
             for (int ks = 0; ks < kHeadDim / 16; ks++) {
                 const uint32_t off = (ks >> 2) * ((kTileBytes / 2) >> 4) + (ks & 3) * 2;  // Q and K halves are both 16 KiB
@@ -288,72 +339,69 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                                        ks > 0, leader);
             }
             tc5::mma_commit_w(bar(kBarSReady + w), leader);
+            if (c.kt == c.un.n_tiles - 1) tc5::mma_commit_w(bar(kBarQEmpty + w), leader);  // last use of this Q tile
+            if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);     // both Q tiles read this K
+            return true;
         };
-        auto issue_pv = [&](int w, int kt) {
-            const uint32_t vst = v_lo + uint32_t((2 * kt + 1) % kSlots) * (kTileBytes >> 4);
-            const int n_steps = tile_n(kt) / 16;
-#pragma unroll 1
-            for (int ks = 0; ks < n_steps; ks++)
-                tc5::mma_f16_ts_lohi_w(tmem + kColO + w * kHeadDim, tmem + kColS + w * kBN + ks * 8, vst + ks * (2048 >> 4),
-                                       kDescHi, kIdescPV, (kt > 0 || ks > 0), leader);
-            tc5::mma_commit_w(bar(kBarPvDone + w), leader);
-        };
-        ok = wait_bar(bar(kBarQFull), 0) && wait_bar(bar(kBarSlotFull), 0);
-        if (ok) {
+        auto issue_pv = [&](int w, const Cursor &c) {
+            const int g = 2 * c.j + 1, slot = g % kSlots;
+            if (!wait_bar(bar(kBarPReady + w), c.j & 1)) return false;
+            if (c.kt == 0 && c.i >= 1 && !wait_bar(bar(kBarOFree + w), (c.i - 1) & 1)) return false;
+            if (w == 0 && !wait_bar(bar(kBarSlotFull + slot), (g / kSlots) & 1)) return false;
             tc5::fence_after_sync();
-            issue_qk(0, 0);
-            ok = wait_bar(bar(kBarQFull + 1), 0);
-        }
-        if (ok) {
-            issue_qk(1, 0);
-            tc5::mma_commit_w(bar(kBarSlotEmpty), leader);  // K(0) has been read by both Q tiles once these complete
-        }
-        for (int kt = 0; kt < n_tiles && ok; kt++) {
-            const bool more = kt + 1 < n_tiles;
-            const int vslot = (2 * kt + 1) % kSlots, kslot = (2 * kt + 2) % kSlots;
+            const uint32_t vst = v_lo + uint32_t(slot) * (kTileBytes >> 4);
+            const int n_steps = tile_n(c) / 16;
 #pragma unroll
-            for (int w = 0; w < kQTiles; w++) {
-                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w);
-                ok = wait_bar(bar(kBarPReady + w), kt & 1);
-                if (ok && w == 0) ok = wait_bar(bar(kBarSlotFull + vslot), ((2 * kt + 1) / kSlots) & 1);
-                if (!ok) break;
-                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w + 1);
-                tc5::fence_after_sync();
-                issue_pv(w, kt);
-                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w + 2);
-                if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + vslot), leader);
-                if (more) {
-                    // S of this Q tile is free again: its P is consumed by the product just issued, in order
-                    if (w == 0) {
-                        ok = wait_bar(bar(kBarSlotFull + kslot), ((2 * kt + 2) / kSlots) & 1);
-                        if (!ok) break;
-                    }
-                    issue_qk(w, kt + 1);
-                    if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + kslot), leader);
+            for (int ks = 0; ks < kBN / 16; ks++)
+                if (ks < n_steps)
+                    tc5::mma_f16_ts_lohi_w(tmem + kColO + w * kHeadDim, tmem + kColS + w * kBN + ks * 8, vst + ks * (2048 >> 4),
+                                           kDescHi, kIdescPV, (c.kt > 0 || ks > 0), leader);
+            tc5::mma_commit_w(bar(kBarPvDone + w), leader);
+            if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);
+            return true;
+        };
+        if (int(blockIdx.x) < n_units) {
+            Cursor cur{int(blockIdx.x), 0, 0, 0, unit_geom(a, blockIdx.x)};
+            ok = issue_qk(0, cur) && issue_qk(1, cur);
+            while (ok) {
+                Cursor nxt = cur;
+                const bool more = advance(nxt);
+#pragma unroll
+                for (int w = 0; w < kQTiles; w++) {
+                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w);
+                    ok = ok && issue_pv(w, cur);
+                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 1);
+                    if (more) ok = ok && issue_qk(w, nxt);
+                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 2);
                 }
-                if (leader) PF_TRACE(1000 + kt * 8 + 4 * w + 3);
+                if (!more) break;
+                cur = nxt;
             }
+            if (!ok && leader) atomicExch(a.error_flag, 1);
         }
-        if (ok) tc5::mma_commit_w(bar(kBarAllDone), leader);
-        else if (leader) atomicExch(a.error_flag, 1);
     } else {
         // =========================================================== softmax warps: one query row per thread
         const int w = warp >> 2;                   // Q tile of this warp
         const int r = tid & (kBM - 1);             // row in the tile = head-in-group * 16 + position-in-tile
         const int hl = r >> 4, qi = r & 15;
-        const int qpos = q_first + w * kQPos + qi;
-        const int qt_first = q_first + w * kQPos;  // first / last position of this Q tile
-        const int qt_last = min(qt_first + kQPos - 1, q_last);
-        const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
         const uint32_t lane_base = tmem + (uint32_t((warp & 3) * 32) << 16);
         const uint32_t colS = lane_base + kColS + w * kBN, colO = lane_base + kColO + w * kHeadDim;
+        int j = 0;  // tiles of the stream seen so far (phase of the S / P / P.V barriers)
+        int i = 0;
+        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, i++) {
+        const Unit un = unit_geom(a, u);
+        const int kvh = un.kvh, t0 = un.t0, klo = un.klo, n_keys = un.n_keys, n_tiles = un.n_tiles;
+        const int qt_first = un.q_first + w * kQPos;  // first / last position of this Q tile
+        const int qt_last = min(qt_first + kQPos - 1, un.q_last);
+        const int qpos = qt_first + qi;
+        const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
 
         float m = sink2, l = 1.0f;  // prefill.metal:162
         for (int kt = 0; kt < n_tiles && ok; kt++) {
-            if (r == 0) PF_TRACE(w * 400 + kt * 8 + 0);
-            ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + w), kt & 1));  // warp-uniform for tcgen05.ld
+            if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 0);
+            ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + w), j & 1));  // warp-uniform for tcgen05.ld
             if (!ok) break;
-            if (r == 0) PF_TRACE(w * 400 + kt * 8 + 1);
+            if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 1);
             tc5::fence_after_sync();
             const int kbase = klo + kt * kBN;
             const int n_cols = min(kBN, (n_keys - kt * kBN + 15) & ~15);  // columns the MMA wrote (same as the issuer)
@@ -444,62 +492,80 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             tc5::tmem_wait_st();
             tc5::fence_before_sync();
             tc5::mbar_arrive(bar(kBarPReady + w));
-            if (r == 0) PF_TRACE(w * 400 + kt * 8 + 2);
+            if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 2);
+            j++;
         }
-        if (r == 0) PF_TRACE(900 + w);
-        // The scores of the last tile prove P.V of tile n-2 done, so a parity wait for tile n-1 is well defined.
-        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone + w), (n_tiles - 1) & 1));
-        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarAllDone), 0));  // the K/V slots become the output tiles
-        if (ok) {
-            // O / l (prefill.metal:255-265) goes out through shared memory: each thread drops its row into a
-            // [8 heads][16 positions][128 B] swizzled tile per 128-byte column block, then one thread per Q tile hands
-            // the tiles to TMA, which writes full lines and clips rows past the prompt.
+        // ---- drain of the unit.  The scores of the last tile proved P.V of the tile before it done, so a parity wait
+        // for the last tile is well defined.
+        if (ok) ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone + w), (j - 1) & 1));
+        if (!ok) break;
+        {
+            // O / l (prefill.metal:255-265) goes out through a staging tile of this Q tile: each thread drops its row
+            // into an [8 heads][16 positions][128 B] swizzled block per 128-byte column block, then one thread hands
+            // the blocks to TMA, which writes full lines and clips rows past the prompt.  bf16 rows fit the two staging
+            // blocks at once; fp32 rows go out in two rounds.  The TMA store of a unit drains while the next unit runs.
             tc5::fence_after_sync();
             const float inv_l = 1.0f / l;
-            const int R = r;  // tile rows ordered [8 heads][16 positions], the order of the output tensor map's box
-            const uint32_t stage_off = kOffKV + w * 4 * kOutBlockBytes;
-            unsigned char *stg = gen + stage_off + R * 128;
-            const int sw = R & 7;
+            const bool f32 = a.out_dtype == kDtypeF32;
+            const uint32_t stage_off = kOffStage + w * 2 * kOutBlockBytes;
+            unsigned char *stg = gen + stage_off + r * 128;
+            const int sw = r & 7;
+            const bool tile_valid = t0 + w * kQPos < a.n_tok;
 #pragma unroll
-            for (int cb = 0; cb < kHeadDim; cb += 32) {
-                uint32_t rr[32];
-                tc5::tmem_ld32(colO + cb, rr);
-                tc5::tmem_wait_ld();
-                if (a.out_dtype == kDtypeF32) {
-                    unsigned char *blk = stg + (cb / 32) * kOutBlockBytes;
+            for (int half = 0; half < 2; half++) {
+                if (half == 0 || f32) {  // the previous store out of these blocks must have read them
+                    if (r == 0) tc5::tma_store_wait_read();
+                    if (w == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four warps of this Q tile only
+                    else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+                }
 #pragma unroll
-                    for (int c = 0; c < 8; c++)
-                        *reinterpret_cast<float4 *>(blk + ((c ^ sw) << 4)) =
-                            make_float4(__uint_as_float(rr[4 * c]) * inv_l, __uint_as_float(rr[4 * c + 1]) * inv_l,
-                                        __uint_as_float(rr[4 * c + 2]) * inv_l, __uint_as_float(rr[4 * c + 3]) * inv_l);
-                } else {
-                    unsigned char *blk = stg + (cb / 64) * kOutBlockBytes;
+                for (int q = 0; q < 2; q++) {
+                    uint32_t rr[32];
+                    tc5::tmem_ld32(colO + half * 64 + q * 32, rr);
+                    tc5::tmem_wait_ld();
+                    if (half == 1 && q == 1) {  // O is in registers: the next unit may overwrite the accumulator
+                        tc5::fence_before_sync();
+                        tc5::mbar_arrive(bar(kBarOFree + w));
+                    }
+                    if (f32) {
+                        unsigned char *blk = stg + q * kOutBlockBytes;
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
-                        uint32_t wd[4];
+                        for (int c = 0; c < 8; c++)
+                            *reinterpret_cast<float4 *>(blk + ((c ^ sw) << 4)) =
+                                make_float4(__uint_as_float(rr[4 * c]) * inv_l, __uint_as_float(rr[4 * c + 1]) * inv_l,
+                                            __uint_as_float(rr[4 * c + 2]) * inv_l, __uint_as_float(rr[4 * c + 3]) * inv_l);
+                    } else {
+                        unsigned char *blk = stg + half * kOutBlockBytes;
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(rr[8 * c + 2 * j]) * inv_l,
-                                                                           __uint_as_float(rr[8 * c + 2 * j + 1]) * inv_l);
-                            wd[j] = *reinterpret_cast<const uint32_t *>(&b);
+                        for (int c = 0; c < 4; c++) {
+                            uint32_t wd[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(rr[8 * c + 2 * e]) * inv_l,
+                                                                               __uint_as_float(rr[8 * c + 2 * e + 1]) * inv_l);
+                                wd[e] = *reinterpret_cast<const uint32_t *>(&b);
+                            }
+                            *reinterpret_cast<uint4 *>(blk + ((4 * q + c) ^ sw) * 16) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
                         }
-                        *reinterpret_cast<uint4 *>(blk + ((((cb & 32) >> 3) + c) ^ sw) * 16) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+                    }
+                }
+                if (half == 1 || f32) {
+                    tc5::fence_proxy_async();
+                    if (w == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                    else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+                    if (r == 0 && tile_valid) {
+                        for (int b = 0; b < 2; b++)
+                            tc5::tma_store_3d(&tm_o, base + stage_off + b * kOutBlockBytes, f32 ? half * 64 + b * 32 : b * 64,
+                                              t0 + w * kQPos, kvh * kGqa);
+                        tc5::tma_store_commit();
                     }
                 }
             }
-            tc5::fence_proxy_async();
-            if (w == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four warps of this Q tile only
-            else asm volatile("bar.sync 2, 128;\n" ::: "memory");
-            if (r == 0 && t0 + w * kQPos < a.n_tok) {
-                const int n_blk = a.out_dtype == kDtypeF32 ? 4 : 2, x_step = a.out_dtype == kDtypeF32 ? 32 : 64;
-                for (int b = 0; b < n_blk; b++)
-                    tc5::tma_store_3d(&tm_o, base + stage_off + b * kOutBlockBytes, b * x_step, t0 + w * kQPos, kvh * kGqa);
-                tc5::tma_store_commit_and_wait_read();
-            }
-        } else if ((tid & 31) == 0) {
-            atomicExch(a.error_flag, 1);  // a wait ran out: report, then leave through the normal teardown
         }
         if (r == 0) PF_TRACE(910 + w);
+        }  // units
+        if (!ok && (tid & 31) == 0) atomicExch(a.error_flag, 1);  // a wait ran out: report, then the normal teardown
+        if (r == 0) tc5::tma_store_wait_read();                    // shared memory must outlive the last store's reads
     }
     tc5::fence_before_sync();
     __syncthreads();
@@ -511,6 +577,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
+int g_sm_count = 148;
 #ifdef FLINT_PF_TRACE
 long long *g_trace_buf = nullptr;
 #endif
@@ -553,6 +620,8 @@ cudaError_t prefill_kernel_setup() {
         if (!fn || qres != cudaDriverEntryPointSuccess) return cudaErrorNotSupported;
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
     return cudaFuncSetAttribute(k_prefill_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
@@ -630,7 +699,8 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     a.out = p.out; a.sinks = p.sinks; a.error_flag = err_flag; a.out_dtype = p.out_dtype;
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
-    const dim3 grid((T + kCtaPos - 1) / kCtaPos, kNHeadKv);
+    const int n_units = ((T + kCtaPos - 1) / kCtaPos) * kNHeadKv;
+    const dim3 grid(n_units < g_sm_count ? n_units : g_sm_count);
     if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
     k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
     if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
