@@ -36,7 +36,8 @@ constexpr int kHist = kNSwa - 1;       // 512 keys of history a sliding-window q
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;               // + 128 * tile
 constexpr int kColO = 256;             // + 128 * tile
-constexpr int kThreadsAttn = (kQTiles * 4 + 2) * 32;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
+constexpr int kThreadsAttn = (kQTiles * 4 + 4) * 32;  // 8 softmax warps, 1 TMA warp, 1 MMA warp, 2 idle warps that
+                                                      // complete the third warpgroup (register reallocation is per warpgroup)
 
 constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB per Q tile: two 64-dim halves of [128 rows][128 B]
 constexpr int kTileBytes = kBN * kHeadDim * 2;  // 32 KiB per K or V tile: two 64-dim halves of [128 keys][128 B]
@@ -257,7 +258,13 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
     const uint32_t tmem = *tmem_slot;
     bool ok = true;
 
-    if (warp == 8) {
+    // Three warps share each SM sub-partition's 16K registers: the compiler's budget is 168 per thread.  The softmax
+    // rows want ~200 (a whole 128-column score row in registers), the TMA / MMA warps few: move registers over.
+    // (each role executes its own setmaxnreg first thing; warps 10 and 11 only complete the third warpgroup)
+    if (warp >= 10) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
+    } else if (warp == 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
         // =========================================================== TMA producer
         if ((tid & 31) == 0) {
             tc5::prefetch_tmap(&tm_q);
@@ -296,6 +303,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             if (!ok) atomicExch(a.error_flag, 1);
         }
     } else if (warp == 9) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
         // =========================================================== MMA issuer (warp-uniform code, one lane issues)
         const uint32_t leader = (tid & 31) == 0;
         constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
@@ -380,6 +388,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             if (!ok && leader) atomicExch(a.error_flag, 1);
         }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;\n");
         // =========================================================== softmax warps: one query row per thread
         const int w = warp >> 2;                   // Q tile of this warp
         const int r = tid & (kBM - 1);             // row in the tile = head-in-group * 16 + position-in-tile
