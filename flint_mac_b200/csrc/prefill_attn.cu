@@ -427,28 +427,26 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 return 1;
             };
 
-            // the whole row of S in registers (one pass over tensor memory), masked where needed
+            // the whole row of S into registers: all loads in flight at once, one wait
             uint32_t sr[kBN];
+#pragma unroll
+            for (int ch = 0; ch < kBN / 32; ch++)
+                if (ch < n_chunks) tc5::tmem_ld32(colS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[ch * 32]));
+            tc5::tmem_wait_ld();
             float mx = -INFINITY;
 #pragma unroll
             for (int ch = 0; ch < kBN / 32; ch++) {
                 if (ch < n_chunks) {
-                    uint32_t t32[32];
-                    tc5::tmem_ld32(colS + ch * 32, t32);
-                    tc5::tmem_wait_ld();
                     const int kind = chunk_kind(ch);
                     float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     if (kind == 0) {
 #pragma unroll
-                        for (int c = 0; c < 32; c++) {
-                            sr[ch * 32 + c] = t32[c];
-                            m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(t32[c]));
-                        }
+                        for (int c = 0; c < 32; c++) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sr[ch * 32 + c]));
                     } else {
 #pragma unroll
                         for (int c = 0; c < 32; c++) {
                             const int col = ch * 32 + c;
-                            const uint32_t v = (kind == 1 && col >= c_lo && col <= c_hi) ? t32[c] : 0xff800000u;  // -inf
+                            const uint32_t v = (kind == 1 && col >= c_lo && col <= c_hi) ? sr[ch * 32 + c] : 0xff800000u;  // -inf
                             sr[ch * 32 + c] = v;
                             m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(v));
                         }
