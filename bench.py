@@ -29,6 +29,11 @@ sys.path.insert(0, ROOT)
 B_PER_GPU, CTX, QKV_DIM, OUT_DIM = 64, 8192, 5120, 4096
 KV_BYTES_PER_KEY = 2048  # K + V, 4 KV heads x 128 dims x fp16, each read once per GQA group
 PREFILL_T = 4000
+# DRAM traffic of one k_decode_attn launch on the default workload, from the committed ncu capture
+# (profiles/k_decode_attn_64x8192.md): 1.074919 GB read + 4.06 MB written.
+DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1074919000 + 4060416
+# Same for k_prefill_attn on the 4000-token workload (profiles/k_prefill_attn_4000tok_swa.md).
+PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41029632 + 1384448
 
 
 def decode_bytes(n_seq: int, n_cached: int) -> int:
@@ -352,7 +357,10 @@ def run_decode(args):
             "tok_per_s": B_PER_GPU * world / (ms_per_step * 1e-3),
             "pct_of_hbm_peak": 100.0 * value / world / hbm_peak,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "frac": achieved / hbm_peak, "traffic": DECODE_NCU_DRAM_BYTES_PER_LAUNCH,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this "
+                                           "workload (profiles/k_decode_attn_64x8192.md)",
+                         "peak_kind": f"of {peak_kind}",
                          "kernel": "k_decode_attn", "kernel_us": kernel_ms_avg * 1e3, "bytes_per_launch": step_bytes},
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": B_PER_GPU * QKV_DIM * 2, "d2h_bytes_per_step": B_PER_GPU * OUT_DIM * 2,
@@ -384,7 +392,8 @@ def run_prefill_only(args):
             "vs_baseline": None, "dtype": "f16 tensor-core products (tcgen05 kind::f16), f32 accumulate/softmax",
             "data": "synthetic", "config": {"workload": pf["workload"], "l2": pf["l2"]},
             "roofline": {"bound": "tensor", "achieved": pf["tflops"], "peak": pf["peak_tflops"], "unit": "TFLOP/s",
-                         "frac": pf["frac"], "traffic": None, "peak_kind": pf["peak_kind"], "kernel": "k_prefill_attn",
+                         "frac": pf["frac"], "traffic": PREFILL_NCU_DRAM_BYTES_PER_LAUNCH, "peak_kind": pf["peak_kind"],
+                         "kernel": "k_prefill_attn",
                          "kernel_us": pf["attn_kernel_us"], "flops_per_launch": pf["algorithmic_flops"]},
             "e2e": {"value": pf["e2e_tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": pf["h2d_bytes_per_step"],
                     "d2h_bytes_per_step": pf["d2h_bytes_per_step"], "us_per_step": pf["e2e_us"]},

@@ -21,6 +21,7 @@ constexpr float kRmsEps = 1e-6f;
 constexpr float kRopeTheta = 10000.0f;
 constexpr int kPartialDim = kHeadDim + 2;      // acc[128], m, l
 constexpr int kRecStride = 132;                // floats between split-K scratch records (16-byte aligned rows)
+constexpr int kMaxParamItems = 640;             // work items that fit the 32 KiB kernel-parameter space
 constexpr int kMergeFan = 16;                  // splits folded by one CTA in the first merge level
 
 constexpr int kDtypeF32 = 0;
@@ -70,6 +71,8 @@ struct CombineParams {
 };
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream);
+// Same kernel with the work list passed by value in the kernel parameters (n_items <= kMaxParamItems): no upload.
+cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream);
 cudaError_t decode_kernel_setup();  // opt-in shared memory size; once per device
 

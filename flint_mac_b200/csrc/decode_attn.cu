@@ -15,6 +15,8 @@
 // the reference's four simdgroups (fused.metal:301-318).  Splits of one (token, KV head) group write fp32 partial
 // records {acc[128], m, l} (fused.metal:324-327); the last CTA of the group to finish (atomic ticket) merges them,
 // so there is no second launch and no spin-wait anywhere.
+#include <cstring>
+
 #include "attn_common.h"
 #include "ptx.cuh"
 
@@ -121,11 +123,10 @@ __device__ __forceinline__ Merged merge_records(const float *rec, int n, int d0,
     return r;
 }
 
-__global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
+__device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &it) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     DecSmem &sm = *reinterpret_cast<DecSmem *>(smem_raw);
 
-    const DecItem it = p.items[blockIdx.x];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int j0 = it.j0, j1 = it.j1;
@@ -392,6 +393,24 @@ __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) 
     }
 }
 
+// The work list either sits in device memory (any length) or, when it is short enough, travels in the kernel's
+// parameter space (large kernel parameters, up to 32 KiB): one wave on a 148-SM part is ~300 items of 48 bytes, so the
+// usual launch needs no host-to-device copy in front of it.
+struct DecItemsParam {
+    DecItem items[kMaxParamItems];
+};
+
+__global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
+    const DecItem it = p.items[blockIdx.x];
+    decode_item(p, it);
+}
+
+__global__ void __launch_bounds__(kThreads, 2) k_decode_attn_p(const __grid_constant__ DecParams p,
+                                                               const __grid_constant__ DecItemsParam ip) {
+    const DecItem it = ip.items[blockIdx.x];
+    decode_item(p, it);
+}
+
 // Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.
 __global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams p) {
     const int tok = blockIdx.x / kNHead, head = blockIdx.x % kNHead, d = threadIdx.x;
@@ -414,12 +433,23 @@ __global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams 
 }  // namespace
 
 cudaError_t decode_kernel_setup() {
-    return cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(DecSmem)));
+    cudaError_t e = cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(DecSmem)));
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_decode_attn_p, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(DecSmem)));
 }
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
     k_decode_attn<<<n_items, kThreads, sizeof(DecSmem), stream>>>(p);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
+    if (n_items <= 0) return cudaSuccess;
+    if (n_items > kMaxParamItems) return cudaErrorInvalidValue;
+    static thread_local DecItemsParam ip;  // copied into the launch by the runtime before this returns
+    memcpy(ip.items, host_items, sizeof(DecItem) * size_t(n_items));
+    k_decode_attn_p<<<n_items, kThreads, sizeof(DecSmem), stream>>>(p, ip);
     return cudaGetLastError();
 }
 

@@ -253,8 +253,9 @@ struct flint_attn {
         int n_groups = 0, n_records = 0, n_subs = 0;
         plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records, n_subs);
         ensure_scratch(n_records, n_subs, n_groups);
+        const bool inline_items = items.size() <= size_t(kMaxParamItems);
         DecParams dp{};
-        dp.items = upload_items(st);
+        dp.items = inline_items ? nullptr : upload_items(st);
         dp.qkv = qkv;
         dp.out = out;
         dp.partial_out = partial_out;
@@ -270,10 +271,11 @@ struct flint_attn {
         dp.qkv_dtype = qkv_dtype; dp.out_dtype = out_dtype;
         dp.mode = mode;
         time_mark(st);
-        CK(launch_decode(dp, int(items.size()), st));
+        if (inline_items) CK(launch_decode_inline(dp, items.data(), int(items.size()), st));
+        else CK(launch_decode(dp, int(items.size()), st));
         time_mark(st);
         launches++;
-        mark_ring_used(dp.items, st);
+        if (!inline_items) mark_ring_used(dp.items, st);
     }
 };
 
