@@ -1,4 +1,4 @@
-// Inline-PTX wrappers for the Blackwell pieces the prefill kernel uses: mbarriers with bounded waits, TMA tensor
+// Inline-PTX wrappers for the Blackwell pieces the prefill kernel uses: mbarriers, TMA tensor
 // copies (no multicast), tensor memory allocation, tcgen05 MMA / load / store, and the shared-memory and
 // instruction descriptors of the 5th-generation tensor core.
 #pragma once
@@ -36,11 +36,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Wait with an iteration limit: returns false when the limit ran out (the caller records an error and leaves
 // through its normal teardown, so tensor memory is always freed and nothing spins forever).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = (1u << 24)) {
-    for (uint32_t i = 0; i < limit; i++)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
-}
+
 
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y, int z) {
@@ -68,43 +64,13 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
-// D[tmem] (+)= A[smem desc] * B[smem desc], one CTA, f16/bf16 inputs, f32 accumulate
-__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same MMA with the descriptors passed as 32-bit halves: the high word is a per-kernel constant and the low word of
-// each K = 16 step differs from the tile's base by a compile-time offset (in 16-byte units), so the issuing thread
-// spends one add per operand instead of rebuilding 64-bit descriptors.
-__device__ __forceinline__ void mma_f16_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
-                                                uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 da, db;\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "mov.b64 da, {%1, %3};\n"
-        "mov.b64 db, {%2, %3};\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// A operand taken from tensor memory (128 lanes = rows, two consecutive K elements per 32-bit column), B from
-// shared memory.
-__device__ __forceinline__ void mma_f16_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi,
-                                                uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n.reg .pred p;\n.reg .b64 db;\n"
-        "setp.ne.b32 p, %5, 0;\n"
-        "mov.b64 db, {%2, %3};\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Warp-uniform issue: the whole warp runs the issuing code (so descriptors and addresses stay in uniform registers)
-// and only the lane with `leader` != 0 executes the MMA / commit.
+// D[tmem] (+)= A * B, one CTA, f16 inputs, f32 accumulate (tcgen05.mma kind::f16).  Descriptors are passed as 32-bit
+// halves: the high word is a per-kernel constant and the low word of each K = 16 step differs from the tile's base by
+// a compile-time offset (in 16-byte units), so issuing costs one add per operand.  Warp-uniform issue: the whole warp
+// runs the issuing code (descriptors and addresses stay in uniform registers) and only the lane with `leader` != 0
+// executes the MMA / commit.
+// A operand taken from tensor memory (128 lanes = rows, two consecutive K elements per 32-bit column), B from shared
+// memory:
 __device__ __forceinline__ void mma_f16_ts_lohi_w(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi,
                                                   uint32_t idesc, uint32_t accumulate, uint32_t leader) {
     asm volatile(
@@ -116,6 +82,7 @@ __device__ __forceinline__ void mma_f16_ts_lohi_w(uint32_t d_tmem, uint32_t a_tm
         "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(leader)
         : "memory");
 }
+// both operands from shared memory:
 __device__ __forceinline__ void mma_f16_ss_lohi_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
                                                   uint32_t idesc, uint32_t accumulate, uint32_t leader) {
     asm volatile(
@@ -128,6 +95,7 @@ __device__ __forceinline__ void mma_f16_ss_lohi_w(uint32_t d_tmem, uint32_t a_lo
         "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(leader)
         : "memory");
 }
+// arrive on an mbarrier when all MMAs issued so far by this thread have completed
 __device__ __forceinline__ void mma_commit_w(uint32_t bar, uint32_t leader) {
     asm volatile(
         "{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
@@ -135,7 +103,12 @@ __device__ __forceinline__ void mma_commit_w(uint32_t bar, uint32_t leader) {
         "r"(leader)
         : "memory");
 }
-// low / high words of smem_desc_sw128
+// Shared-memory matrix descriptor, 128-byte swizzle, tile base aligned to 1024 bytes, as low / high 32-bit words.
+//   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
+//   bits 32-45 stride-dimension byte offset >> 4      bits 46-47 descriptor version (1)      bits 61-63 swizzle (2 = 128 B)
+// K-major operand (rows of 64 halves = 128 B, K contiguous): SBO = 1024 (next group of 8 rows); LBO unused.
+// MN-major operand (rows of 64 halves = 128 B, M/N contiguous, one row per K index): LBO = distance between
+// consecutive 64-wide M/N blocks, SBO = 1024 (next group of 8 K indices).
 __device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
     return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
@@ -152,15 +125,10 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t sr
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
-__device__ __forceinline__ void tma_store_commit_and_wait_read() {
-    asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
-}
+
 
 // arrive on an mbarrier when all previously issued MMAs of this thread have completed
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
+
 
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (warp%4)*32 + i
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -194,17 +162,7 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
-// ------------------------------------------------------------------ descriptors
-// Shared-memory matrix descriptor, 128-byte swizzle, tile base aligned to 1024 bytes.
-//   bits  0-13 start address >> 4      bits 16-29 leading-dimension byte offset >> 4
-//   bits 32-45 stride-dimension byte offset >> 4      bits 46-47 descriptor version (1)      bits 61-63 swizzle (2 = 128 B)
-// K-major operand (rows of 64 halves = 128 B, K contiguous): SBO = 1024 (next group of 8 rows); LBO unused.
-// MN-major operand (rows of 64 halves = 128 B, M/N contiguous, one row per K index): LBO = distance between
-// consecutive 64-wide M/N blocks, SBO = 1024 (next group of 8 K indices).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return uint64_t((addr & 0x3FFFFu) >> 4) | (uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-           (uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
-}
+// ------------------------------------------------------------------ instruction descriptor
 // Instruction descriptor for kind::f16: f16 A and B, f32 accumulator, dense.
 //   bits 4-5 D format (1 = f32)  7-9 A format (0 = f16)  10-12 B format  15 A major (1 = MN)  16 B major  17-22 N>>3  24-28 M>>4
 __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, int a_mn_major, int b_mn_major) {
