@@ -44,7 +44,10 @@ constexpr int kTileBytes = kBN * kHeadDim * 2;  // 32 KiB per K or V tile: two 6
 constexpr int kOffQ = 0;
 constexpr int kOffKV = kOffQ + kQTiles * kQBytes;
 constexpr int kOutBlockBytes = kQPos * kGqa * 128;  // one 128-byte-wide column block of one Q tile's output
-constexpr int kOffStage = kOffKV + kSlots * kTileBytes;  // output staging: two column blocks per Q tile
+constexpr int kPBytes = kBM * kBN * 2;        // 32 KiB per P tile (two 64-key halves of [128 rows][128 B]); shares the
+                                              // staging block of its Q tile with the output rows of the unit's drain
+constexpr int kOffStage = kOffKV + kSlots * kTileBytes;  // per Q tile 32 KiB: P tiles, and the output rows at the end of a unit
+static_assert(kPBytes == 2 * kOutBlockBytes, "P and the output staging share one block per Q tile");
 constexpr int kOffBar = kOffStage + kQTiles * 2 * kOutBlockBytes;
 constexpr int kSmemBytes = kOffBar + 256;  // 229632 B: one CTA per SM
 
@@ -182,6 +185,12 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
     }
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // Barriers (8 bytes each, at kOffBar): the warps only ever talk through these.  Every barrier completes one phase
 // per use, and each waiter counts its own uses, so the phase parities stay valid across the work units of a CTA.
 enum {
@@ -193,7 +202,8 @@ enum {
     kBarPReady = kBarSReady + 2,            // [2] softmax warps -> MMA warp: P is in tensor memory, S consumed (128 arrivals)
     kBarPvDone = kBarPReady + 2,            // [2] tensor core -> softmax warps: O += P.V of the current tile
     kBarOFree = kBarPvDone + 2,             // [2] softmax warps -> MMA warp: O of the finished unit has been read out (128)
-    kNumBars = kBarOFree + 2
+    kBarSFree = kBarOFree + 2,              // [2] softmax warps -> MMA warp: S of the current tile is in registers (128)
+    kNumBars = kBarSFree + 2
 };
 
 // A work unit: 32 consecutive query positions (two Q tiles of 16 positions x 8 heads) of one KV head.
@@ -243,7 +253,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; i++) {
-            const bool many = (i >= kBarPReady && i < kBarPReady + 2) || (i >= kBarOFree && i < kBarOFree + 2);
+            const bool many = (i >= kBarPReady && i < kBarPReady + 2) || (i >= kBarOFree && i < kBarOFree + 4);
             tc5::mbar_init(bar(i), many ? kBM : 1);
         }
         tc5::mbar_fence_init();
@@ -309,6 +319,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
         constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);  // A = P (tensor memory), B = V (MN-major)
         const uint32_t q_lo = tc5::desc_lo(base + kOffQ, 16);
+        const uint32_t p_lo = tc5::desc_lo(base + kOffStage, 16);            // P tile: K-major, two 64-key halves
         const uint32_t k_lo = tc5::desc_lo(base + kOffKV, 16);               // K tile: K-major, two 64-dim halves
         const uint32_t v_lo = tc5::desc_lo(base + kOffKV, kTileBytes / 2);   // V tile: MN-major, LBO = the other 64 dims
         // The key tiles of all units of this CTA form one stream; tile j of the stream has its K in ring use 2j and
@@ -335,6 +346,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         };
         auto issue_qk = [&](int w, const Cursor &c) {
             const int g = 2 * c.j, slot = g % kSlots;
+            if (c.j >= 1 && !wait_bar(bar(kBarSFree + w), (c.j - 1) & 1)) return false;  // the previous scores are read out
             if (c.kt == 0 && !wait_bar(bar(kBarQFull + w), c.i & 1)) return false;
             if (w == 0 && !wait_bar(bar(kBarSlotFull + slot), (g / kSlots) & 1)) return false;
             tc5::fence_after_sync();
@@ -362,8 +374,9 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
 #pragma unroll
             for (int ks = 0; ks < kBN / 16; ks++)
                 if (ks < n_steps)
-                    tc5::mma_f16_ts_lohi_w(tmem + kColO + w * kHeadDim, tmem + kColS + w * kBN + ks * 8, vst + ks * (2048 >> 4),
-                                           kDescHi, kIdescPV, (c.kt > 0 || ks > 0), leader);
+                    tc5::mma_f16_ss_lohi_w(tmem + kColO + w * kHeadDim,
+                                           p_lo + w * (kPBytes >> 4) + (ks >> 2) * ((kPBytes / 2) >> 4) + (ks & 3) * 2,
+                                           vst + ks * (2048 >> 4), kDescHi, kIdescPV, (c.kt > 0 || ks > 0), leader);
             tc5::mma_commit_w(bar(kBarPvDone + w), leader);
             if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);
             return true;
@@ -374,12 +387,17 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             while (ok) {
                 Cursor nxt = cur;
                 const bool more = advance(nxt);
+                // The next scores are issued as soon as the current ones have been read into registers, so they are
+                // computed while the softmax of the current tile runs; P.V follows when P has been written.
 #pragma unroll
                 for (int w = 0; w < kQTiles; w++) {
                     if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w);
-                    ok = ok && issue_pv(w, cur);
-                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 1);
                     if (more) ok = ok && issue_qk(w, nxt);
+                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 1);
+                }
+#pragma unroll
+                for (int w = 0; w < kQTiles; w++) {
+                    ok = ok && issue_pv(w, cur);
                     if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 2);
                 }
                 if (!more) break;
@@ -427,31 +445,49 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 return 1;
             };
 
+            // Band-edge tiles (the first and the last of a unit) first get their invisible scores overwritten with -inf
+            // in tensor memory by a small loop; after that every tile runs the same straight-line code, which stays
+            // small enough for the instruction cache.
+            if (chunk_kind(0) != 0 || chunk_kind(n_chunks - 1) != 0) {
+#pragma unroll 1
+                for (int ch = 0; ch < n_chunks; ch++) {
+                    const int kind = chunk_kind(ch);
+                    if (kind == 0) continue;
+                    uint32_t t32[32];
+                    if (kind == 1) {
+                        tc5::tmem_ld32(colS + ch * 32, t32);
+                        tc5::tmem_wait_ld();
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c++) {
+                        const int col = ch * 32 + c;
+                        if (kind == 2 || col < c_lo || col > c_hi) t32[c] = 0xff800000u;  // -inf
+                    }
+                    tc5::tmem_st32(colS + ch * 32, t32);
+                }
+                tc5::tmem_wait_st();
+            }
             // the whole row of S into registers: all loads in flight at once, one wait
             uint32_t sr[kBN];
 #pragma unroll
             for (int ch = 0; ch < kBN / 32; ch++)
                 if (ch < n_chunks) tc5::tmem_ld32(colS + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[ch * 32]));
             tc5::tmem_wait_ld();
+            tc5::fence_before_sync();
+            tc5::mbar_arrive(bar(kBarSFree + w));  // S is in registers: the next scores may overwrite it
             float mx = -INFINITY;
 #pragma unroll
             for (int ch = 0; ch < kBN / 32; ch++) {
                 if (ch < n_chunks) {
-                    const int kind = chunk_kind(ch);
-                    float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    if (kind == 0) {
+                    float t4[4];
 #pragma unroll
-                        for (int c = 0; c < 32; c++) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sr[ch * 32 + c]));
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 32; c++) {
-                            const int col = ch * 32 + c;
-                            const uint32_t v = (kind == 1 && col >= c_lo && col <= c_hi) ? sr[ch * 32 + c] : 0xff800000u;  // -inf
-                            sr[ch * 32 + c] = v;
-                            m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(v));
-                        }
-                    }
-                    mx = fmaxf(mx, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));
+                    for (int c = 0; c < 4; c++)
+                        t4[c] = max3(fmaxf(__uint_as_float(sr[ch * 32 + 8 * c]), __uint_as_float(sr[ch * 32 + 8 * c + 1])),
+                                     max3(__uint_as_float(sr[ch * 32 + 8 * c + 2]), __uint_as_float(sr[ch * 32 + 8 * c + 3]),
+                                          __uint_as_float(sr[ch * 32 + 8 * c + 4])),
+                                     max3(__uint_as_float(sr[ch * 32 + 8 * c + 5]), __uint_as_float(sr[ch * 32 + 8 * c + 6]),
+                                          __uint_as_float(sr[ch * 32 + 8 * c + 7])));
+                    mx = fmaxf(mx, fmaxf(fmaxf(t4[0], t4[1]), fmaxf(t4[2], t4[3])));
                 }
             }
             // lazy rescale: keep the old reference maximum unless the row maximum outgrew it by more than 2^8
@@ -464,8 +500,20 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 m = mx;
                 l *= corr;
             }
+            if (j >= 1) {
+                // O and the P buffer belong to the tensor core until P.V of the previous tile of the stream is done
+                // (it usually is by now: it was issued a whole softmax ago)
+                ok = __all_sync(0xffffffffu, wait_bar(bar(kBarPvDone + w), (j - 1) & 1));
+                if (!ok) break;
+                tc5::fence_after_sync();
+            }
+            if (kt == 0 && i >= 1) {  // the P buffer doubles as output staging: the previous unit's store must have read it
+                if (r == 0) tc5::tma_store_wait_read();
+                if (w == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                else asm volatile("bar.sync 2, 128;\n" ::: "memory");
+            }
             if (kt >= 1 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // rare.  These scores were computed after P.V of the previous tile (same issue order), so O is idle.
+                // rare
 #pragma unroll 1
                 for (int cb = 0; cb < kHeadDim; cb += 32) {
                     uint32_t rr[32];
@@ -475,8 +523,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                     for (int c = 0; c < 32; c++) rr[c] = __float_as_uint(__uint_as_float(rr[c]) * corr);
                     tc5::tmem_st32(colO + cb, rr);
                 }
+                tc5::tmem_wait_st();
+                tc5::fence_before_sync();
             }
-            // probabilities: P (half, two keys per 32-bit column) goes over the first half of S in tensor memory
+            // probabilities: P (half) goes to this Q tile's shared-memory block in the K-major 128-byte-swizzled layout
+            // of an MMA A operand: two 64-key halves of [128 rows][128 B]
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ch = 0; ch < kBN / 32; ch++) {
@@ -492,12 +543,15 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                         pw[c >> 1] = pack_half2(p0, p1);
                         pw[(c >> 1) + 1] = pack_half2(p2, p3);
                     }
-                    tc5::tmem_st16(colS + ch * 16, pw);
+                    unsigned char *prow = gen + kOffStage + w * kPBytes + (ch >> 1) * (kPBytes / 2) + r * 128;
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        *reinterpret_cast<uint4 *>(prow + ((((ch & 1) * 4 + q) ^ (r & 7)) << 4)) =
+                            make_uint4(pw[4 * q], pw[4 * q + 1], pw[4 * q + 2], pw[4 * q + 3]);
                 }
             }
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            tc5::tmem_wait_st();
-            tc5::fence_before_sync();
+            tc5::fence_proxy_async();
             tc5::mbar_arrive(bar(kBarPReady + w));
             if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 2);
             j++;
