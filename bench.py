@@ -432,15 +432,40 @@ def run_longctx(args):
     stream = torch.cuda.current_stream().cuda_stream
     for c in range(copies):
         h.set_pos(c, S)
+    peer = world > 1 and args.exchange == "peer"
+    if peer:
+        import torch.distributed as dist
+
+        handles = [None] * world
+        dist.all_gather_object(handles, h.xchg_create(1))
+        h.xchg_connect(handles)
+        barrier(world)
+
+    def step_nccl(i):
+        h.decode_partial_dev(0, [i % copies], qkv[i], fa.BF16, part, stream)
+        gathered = fdist.gather_partials(part)
+        h.combine_dev(0, 1, world, gathered, out, fa.BF16, stream)
 
     def step(i):
         c = i % copies
         if world == 1:
             h.decode_dev(0, [c], qkv[i], fa.BF16, out, fa.BF16, stream)
+        elif peer:
+            h.decode_xchg_post_dev(0, [c], qkv[i], fa.BF16, stream)
+            h.combine_xchg_dev(0, 1, out, fa.BF16, stream)
         else:
-            h.decode_partial_dev(0, [c], qkv[i], fa.BF16, part, stream)
-            gathered = fdist.gather_partials(part)
-            h.combine_dev(0, 1, world, gathered, out, fa.BF16, stream)
+            step_nccl(i)
+
+    if peer:  # the two exchanges must agree before anything is timed
+        step_nccl(0)
+        want = out.float().clone()
+        barrier(world)
+        step(0)
+        torch.cuda.synchronize()
+        h.check()
+        if float((out.float() - want).abs().max()) > 1e-2:
+            raise SystemExit("peer-memory exchange disagrees with the NCCL exchange")
+        barrier(world)
 
     for i in range(args.warmup):
         step(i)
@@ -469,7 +494,11 @@ def run_longctx(args):
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16 KV, f16 tensor-core products, f32 accumulate/softmax",
                 "data": "synthetic",
                 "config": {"workload": "long-context decode: 1 sequence x 131072 cached tokens, full layer, KV range "
-                                       "sharded over the ranks, partial (O,m,l) all-gathered (NCCL) and merged",
+                                       "sharded over the ranks, partial (O,m,l) records " +
+                                       ("stored into every rank's memory by the decode kernel (NVLink peer stores) "
+                                        "and merged by a kernel that waits on the ranks' step flags" if peer else
+                                        "all-gathered (NCCL) and merged"),
+                           "exchange": "peer" if peer else ("nccl" if world > 1 else "none"),
                            "kv_copies_rotated": copies, "l2": "rotating over KV copies larger than L2 in total"},
                 "tok_per_s": 1.0 / (ms * 1e-3), "us_per_token": ms * 1e3,
                 "roofline": {"bound": "hbm", "achieved": per_gpu / (kernel_us * 1e-6) / 1e9, "peak": hbm_peak, "unit": "GB/s",
@@ -608,6 +637,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "ragged"])
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="longctx on several GPUs: partial records through peer memory by the kernels, or by NCCL")
     ap.add_argument("--skip-prefill", action="store_true", help="decode workload only (profiling runs)")
     ap.add_argument("--skip-cpu", action="store_true", help="shortest possible CPU baseline sample (profiling runs)")
     args = ap.parse_args()

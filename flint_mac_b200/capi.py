@@ -43,6 +43,14 @@ SYMBOLS = {
                                                   C.c_int32, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
     "flint_attn_combine_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_int32,
                                            C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_xchg_create": (C.c_int32, [C.c_void_p, C.c_int32, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_xchg_connect": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_xchg_base": (C.c_void_p, [C.c_void_p]),
+    "flint_attn_xchg_connect_local": (C.c_int32, [C.c_void_p, C.POINTER(C.c_void_p), C.c_char_p, C.c_int32]),
+    "flint_attn_decode_xchg_post_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_void_p,
+                                                    C.c_int32, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_combine_xchg_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
+                                                C.c_char_p, C.c_int32]),
     "flint_attn_prefill": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
                                        C.c_int32, C.c_char_p, C.c_int32]),
     "flint_attn_prefill_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
@@ -218,6 +226,35 @@ class Attn:
 
     def combine_dev(self, layer, n, n_parts, partials_dev, out_dev, out_dtype, stream: int = 0):
         self._call("flint_attn_combine_dev", layer, n, n_parts, _ptr(partials_dev), _ptr(out_dev), out_dtype, stream)
+
+    # ---- exchange of partial records through peer memory (KV-range sharding on the GPUs of one node)
+    IPC_HANDLE_BYTES = 64
+
+    def xchg_create(self, n_max: int) -> bytes:
+        """Allocate this rank's gather buffer; returns its CUDA IPC handle for the other ranks' xchg_connect."""
+        h = C.create_string_buffer(self.IPC_HANDLE_BYTES)
+        self._call("flint_attn_xchg_create", n_max, C.cast(h, C.c_void_p))
+        return h.raw
+
+    def xchg_connect(self, handles):
+        """handles: one IPC handle per rank, in rank order (this rank's own entry is not opened)."""
+        blob = b"".join(handles)
+        buf = C.create_string_buffer(blob, len(blob))
+        self._call("flint_attn_xchg_connect", C.cast(buf, C.c_void_p))
+
+    def xchg_base(self) -> int:
+        return int(self._lib.flint_attn_xchg_base(self._h) or 0)
+
+    def xchg_connect_local(self, bases):
+        """Ranks that are handles of one process: bases[r] = rank r's xchg_base()."""
+        arr = (C.c_void_p * len(bases))(*bases)
+        self._call("flint_attn_xchg_connect_local", arr)
+
+    def decode_xchg_post_dev(self, layer, seqs, qkv_dev, qkv_dtype, stream: int = 0):
+        self._call("flint_attn_decode_xchg_post_dev", layer, len(seqs), _i32(seqs), _ptr(qkv_dev), qkv_dtype, stream)
+
+    def combine_xchg_dev(self, layer, n, out_dev, out_dtype, stream: int = 0):
+        self._call("flint_attn_combine_xchg_dev", layer, n, _ptr(out_dev), out_dtype, stream)
 
     def prefill_dev(self, layer, seq, n_tok, qkv_dev, qkv_dtype, out_dev, out_dtype, stream: int = 0):
         self._call("flint_attn_prefill_dev", layer, seq, n_tok, _ptr(qkv_dev), qkv_dtype, _ptr(out_dev), out_dtype,

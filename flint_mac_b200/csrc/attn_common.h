@@ -21,6 +21,7 @@ constexpr float kRmsEps = 1e-6f;
 constexpr float kRopeTheta = 10000.0f;
 constexpr int kPartialDim = kHeadDim + 2;      // acc[128], m, l
 constexpr int kRecStride = 132;                // floats between split-K scratch records (16-byte aligned rows)
+constexpr int kMaxPeers = 8;                    // ranks of a KV-range-sharded sequence (one NVSwitch domain)
 constexpr int kMaxParamItems = 640;             // work items that fit the 32 KiB kernel-parameter space
 constexpr int kMergeFan = 16;                  // splits folded by one CTA in the first merge level
 
@@ -60,7 +61,16 @@ struct DecParams {
     int kv_lo;              // position held by slot 0 of a (sharded) full layer
     int has_rope;
     int qkv_dtype, out_dtype;
-    int mode;               // 0: final output with sink; 1: partial record output
+    int mode;               // 0: final output with sink; 1: partial record output; 2: partial records to every peer
+    // mode 2 (KV-range sharding with a peer-memory exchange): this device's record of token t and head h goes to
+    // peer_out[r] + (t * 32 + h) * 130 for every peer r (each points at this rank's slot in that peer's gather
+    // buffer); when the last (token, KV head) group of the launch has written, peer_flag[r][rank] = step.
+    float *peer_out[kMaxPeers];
+    uint32_t *peer_flag[kMaxPeers];
+    int n_peers, rank;
+    uint32_t step;
+    int *groups_done;       // one counter, zero between launches
+    int n_groups;
 };
 
 struct CombineParams {
@@ -68,6 +78,11 @@ struct CombineParams {
     const float *sinks;
     void *out;              // [n][4096]
     int n, n_parts, out_dtype;
+    int part_stride;        // floats between consecutive parts (n * 32 * 130 when packed)
+    // peer-memory exchange only: wait (bounded) until flags[r] == step for every part before reading
+    const uint32_t *flags;  // null: do not wait
+    uint32_t step;
+    int *error_flag;
 };
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream);

@@ -94,6 +94,28 @@ struct Merged {
     float a[8];
 };
 
+// Mode 1 writes this device's record to partial_out; mode 2 writes it into every peer's gather buffer over NVLink
+// (plain peer stores; the data lands in the peer's memory, so the peer reads it locally).
+__device__ __forceinline__ int n_record_targets(const DecParams &p) { return p.mode == 2 ? p.n_peers : 1; }
+__device__ __forceinline__ float *record_target(const DecParams &p, int t, int tok, int head) {
+    float *base = p.mode == 2 ? p.peer_out[t] : p.partial_out;
+    return base + (size_t(tok) * kNHead + head) * kPartialDim;
+}
+
+// Mode 2: after a (token, KV head) group has written its records everywhere, count it; the last group of the launch
+// publishes the step number in every peer's flag word for this rank (release at system scope).
+__device__ __forceinline__ void publish_group(const DecParams &p, int tid) {
+    if (p.mode != 2) return;
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0 && atomicAdd(p.groups_done, 1) == p.n_groups - 1) {
+        *p.groups_done = 0;
+        __threadfence_system();
+        for (int t = 0; t < p.n_peers; t++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.peer_flag[t] + p.rank), "r"(p.step) : "memory");
+    }
+}
+
 // Fold n partial records of one head (fused.metal:332-350): M = max m_s (and the sink), L = sum l_s e^(m_s - M)
 // (+ e^(sink - M)), a = sum acc_s e^(m_s - M).  `rec` points at record 0 of this thread's head; consecutive records
 // of the same head are kGqa * kRecStride floats apart.  The thread owns dims [d0, d0 + 8).  Loads are independent
@@ -323,16 +345,21 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
                       A * cs / (L * cs + fast_exp2(sink2 - Mf)));
         } else if (direct) {
             // this device's only record for the token: {acc[128], m, l}, m in natural-log units (fused.metal:324-327)
-            float *rec = p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim;
-            rec[d] = A;
-            if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
+            for (int t = 0; t < n_record_targets(p); t++) {
+                float *rec = record_target(p, t, it.tok, head);
+                rec[d] = A;
+                if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
+            }
         } else {
             float *rec = rec_base + size_t(h) * kRecStride;
             rec[d] = A;
             if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
         }
     }
-    if (direct) return;
+    if (direct) {
+        publish_group(p, tid);
+        return;
+    }
 
     // ---- split-K merge (fused.metal:332-350), done by whichever CTA finishes last -- no second launch, no waiting.
     // Two levels, so that a long sequence cut into hundreds of splits is not merged by a single CTA: the last CTA of
@@ -386,10 +413,13 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
             *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
         }
     } else {
-        float *rec = p.partial_out + (size_t(it.tok) * kNHead + head) * kPartialDim;  // 130-float public record
+        for (int t = 0; t < n_record_targets(p); t++) {
+            float *rec = record_target(p, t, it.tok, head);  // 130-float public record
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) *reinterpret_cast<float2 *>(rec + md + j) = make_float2(r.a[j], r.a[j + 1]);
-        if (md == 0) { rec[kHeadDim] = r.M; rec[kHeadDim + 1] = r.L; }
+            for (int j = 0; j < 8; j += 2) *reinterpret_cast<float2 *>(rec + md + j) = make_float2(r.a[j], r.a[j + 1]);
+            if (md == 0) { rec[kHeadDim] = r.M; rec[kHeadDim + 1] = r.L; }
+        }
+        publish_group(p, tid);
     }
 }
 
@@ -411,21 +441,44 @@ __global__ void __launch_bounds__(kThreads, 2) k_decode_attn_p(const __grid_cons
     decode_item(p, it);
 }
 
-// Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.
+// Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.  With a
+// peer-memory exchange the records were stored by the other GPUs; the CTA first waits until every rank has published
+// this step.  The wait is bounded (about a second); when it runs out the kernel records an error and returns.
+constexpr long long kPeerWaitCycles = 2000000000LL;  // about a second at the part's clocks
 __global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams p) {
     const int tok = blockIdx.x / kNHead, head = blockIdx.x % kNHead, d = threadIdx.x;
+    if (p.flags) {
+        __shared__ int timed_out;
+        if (d == 0) {
+            timed_out = 0;
+            for (int r = 0; r < p.n_parts && !timed_out; r++) {
+                uint32_t v = 0;
+                const long long t0 = clock64();
+                for (;;) {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p.flags + r) : "memory");
+                    // a peer may already be one step ahead (it writes the other record buffer then)
+                    if (int32_t(v - p.step) >= 0 || clock64() - t0 > kPeerWaitCycles) break;
+                    __nanosleep(200);
+                }
+                if (int32_t(v - p.step) < 0) timed_out = 1;
+            }
+            if (timed_out) atomicExch(p.error_flag, 3);
+        }
+        __syncthreads();
+        if (timed_out) return;
+    }
     const float sink = p.sinks[head];
     float M = sink;
     for (int s = 0; s < p.n_parts; s++)
-        M = fmaxf(M, p.partials[((size_t(s) * p.n + tok) * kNHead + head) * kPartialDim + kHeadDim]);
+        M = fmaxf(M, __ldcg(p.partials + size_t(s) * p.part_stride + (size_t(tok) * kNHead + head) * kPartialDim + kHeadDim));
     float L = __expf(sink - M), A = 0.f;
     for (int s = 0; s < p.n_parts; s++) {
-        const float *rec = p.partials + ((size_t(s) * p.n + tok) * kNHead + head) * kPartialDim;
-        const float ls = rec[kHeadDim + 1];
+        const float *rec = p.partials + size_t(s) * p.part_stride + (size_t(tok) * kNHead + head) * kPartialDim;
+        const float ls = __ldcg(rec + kHeadDim + 1);
         if (ls == 0.f) continue;
-        const float c = __expf(rec[kHeadDim] - M);
+        const float c = __expf(__ldcg(rec + kHeadDim) - M);
         L += ls * c;
-        A += rec[d] * c;
+        A += __ldcg(rec + d) * c;
     }
     store_out(p.out, p.out_dtype, size_t(tok) * kQDim + head * kHeadDim + d, A / L);
 }

@@ -126,6 +126,14 @@ struct flint_attn {
     PrefillWorkspace pf;
     int64_t launches = 0;
     std::vector<DecItem> items;
+    // peer-memory exchange of partial records (KV-range sharding): one cudaMalloc block per rank, opened by the
+    // others through CUDA IPC.  Layout: [flags: kMaxPeers words | error word | groups-done counter] in the first 256
+    // bytes, then records [2 buffers][ranks][xchg_n][32][130] floats (buffers alternate per step).
+    unsigned char *xchg = nullptr;
+    unsigned char *xchg_peer[kMaxPeers] = {};
+    bool xchg_opened[kMaxPeers] = {};
+    int xchg_n = 0;
+    uint32_t xchg_step = 0;
     // optional device timing of the attention kernels alone (events around each launch)
     bool timing = false;
     std::vector<cudaEvent_t> ev_pool;
@@ -143,6 +151,9 @@ struct flint_attn {
             if (ring_ev[i]) cudaEventDestroy(ring_ev[i]);
         }
         prefill_workspace_free(pf);
+        for (int r = 0; r < kMaxPeers; r++)
+            if (xchg_opened[r]) cudaIpcCloseMemHandle(xchg_peer[r]);
+        cudaFree(xchg);
         for (cudaEvent_t e : ev_pool) cudaEventDestroy(e);
         if (stream) cudaStreamDestroy(stream);
     }
@@ -270,6 +281,19 @@ struct flint_attn {
         dp.has_rope = L.has_rope;
         dp.qkv_dtype = qkv_dtype; dp.out_dtype = out_dtype;
         dp.mode = mode;
+        if (mode == 2) {
+            const size_t rec_bytes = size_t(xchg_n) * kNHead * kPartialDim * sizeof(float);
+            const size_t buf_off = 256 + size_t(xchg_step & 1) * kv_ranks * rec_bytes + size_t(kv_rank) * rec_bytes;
+            for (int r = 0; r < kv_ranks; r++) {
+                dp.peer_out[r] = reinterpret_cast<float *>(xchg_peer[r] + buf_off);
+                dp.peer_flag[r] = reinterpret_cast<uint32_t *>(xchg_peer[r]);
+            }
+            dp.n_peers = kv_ranks;
+            dp.rank = kv_rank;
+            dp.step = xchg_step;
+            dp.groups_done = reinterpret_cast<int *>(xchg + (kMaxPeers + 1) * sizeof(uint32_t));
+            dp.n_groups = n_groups;
+        }
         time_mark(st);
         if (inline_items) CK(launch_decode_inline(dp, items.data(), int(items.size()), st));
         else CK(launch_decode(dp, int(items.size()), st));
@@ -430,6 +454,95 @@ int32_t flint_attn_decode_partial_dev(flint_attn *a, int32_t layer, int32_t n, c
     API_CATCH(-1)
 }
 
+int32_t flint_attn_xchg_create(flint_attn *a, int32_t n_max, void *ipc_handle_out, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    if (a->xchg) throw std::runtime_error("exchange buffer already created");
+    if (n_max < 1 || n_max > a->max_seqs) throw std::runtime_error("n_max out of range");
+    if (a->kv_ranks > kMaxPeers) throw std::runtime_error("at most 8 ranks can share a sequence");
+    const size_t bytes = 256 + 2 * size_t(a->kv_ranks) * n_max * kNHead * kPartialDim * sizeof(float);
+    CK(cudaMalloc(&a->xchg, bytes));
+    CK(cudaMemset(a->xchg, 0, bytes));
+    a->xchg_n = n_max;
+    a->xchg_step = 0;
+    a->xchg_peer[a->kv_rank] = a->xchg;
+    if (ipc_handle_out) {
+        cudaIpcMemHandle_t h;
+        CK(cudaIpcGetMemHandle(&h, a->xchg));
+        static_assert(sizeof(h) == FLINT_ATTN_IPC_HANDLE_BYTES, "IPC handle size");
+        memcpy(ipc_handle_out, &h, sizeof(h));
+    }
+    CK(cudaDeviceSynchronize());
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_xchg_connect(flint_attn *a, const void *ipc_handles, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    if (!a->xchg) throw std::runtime_error("create the exchange buffer first");
+    for (int r = 0; r < a->kv_ranks; r++) {
+        if (r == a->kv_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const char *>(ipc_handles) + size_t(r) * sizeof(h), sizeof(h));
+        void *ptr = nullptr;
+        CK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        a->xchg_peer[r] = static_cast<unsigned char *>(ptr);
+        a->xchg_opened[r] = true;
+    }
+    return 0;
+    API_CATCH(-1)
+}
+
+void *flint_attn_xchg_base(flint_attn *a) { return a->xchg; }
+
+int32_t flint_attn_xchg_connect_local(flint_attn *a, void *const *peer_bases, char *err, int32_t err_len) {
+    API_TRY
+    if (!a->xchg) throw std::runtime_error("create the exchange buffer first");
+    for (int r = 0; r < a->kv_ranks; r++)
+        if (r != a->kv_rank) a->xchg_peer[r] = static_cast<unsigned char *>(peer_bases[r]);
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_decode_xchg_post_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs,
+                                        const void *qkv_dev, int32_t qkv_dtype, void *cuda_stream, char *err,
+                                        int32_t err_len) {
+    API_TRY
+    if (!a->xchg) throw std::runtime_error("create and connect the exchange buffer first");
+    for (int r = 0; r < a->kv_ranks; r++)
+        if (!a->xchg_peer[r]) throw std::runtime_error("exchange buffer not connected to every rank");
+    if (n > a->xchg_n) throw std::runtime_error("batch larger than the exchange buffer");
+    if (a->layer(layer).is_swa) throw std::runtime_error("sliding-window layers are not sharded: use decode_dev");
+    a->xchg_step++;
+    a->decode_dev(layer, n, seqs, qkv_dev, qkv_dtype, nullptr, 0, nullptr, 2, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_combine_xchg_dev(flint_attn *a, int32_t layer, int32_t n, void *out_dev, int32_t out_dtype,
+                                    void *cuda_stream, char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    Layer &L = a->layer(layer);
+    if (!a->xchg || a->xchg_step == 0) throw std::runtime_error("nothing was posted");
+    if (n <= 0 || n > a->xchg_n) throw std::runtime_error("bad combine shape");
+    if (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16) throw std::runtime_error("bad out dtype");
+    const size_t rec_floats = size_t(a->xchg_n) * kNHead * kPartialDim;
+    CombineParams cp{};
+    cp.partials = reinterpret_cast<const float *>(a->xchg + 256) + size_t(a->xchg_step & 1) * a->kv_ranks * rec_floats;
+    cp.sinks = L.sinks; cp.out = out_dev;
+    cp.n = n; cp.n_parts = a->kv_ranks; cp.out_dtype = out_dtype;
+    cp.part_stride = int(rec_floats);
+    cp.flags = reinterpret_cast<const uint32_t *>(a->xchg);
+    cp.step = a->xchg_step;
+    cp.error_flag = reinterpret_cast<int *>(a->xchg + kMaxPeers * sizeof(uint32_t));
+    CK(launch_combine(cp, cudaStream_t(cuda_stream)));
+    a->launches++;
+    return 0;
+    API_CATCH(-1)
+}
+
 int32_t flint_attn_combine_dev(flint_attn *a, int32_t layer, int32_t n, int32_t n_parts, const float *partials_dev,
                                void *out_dev, int32_t out_dtype, void *cuda_stream, char *err, int32_t err_len) {
     API_TRY
@@ -437,7 +550,10 @@ int32_t flint_attn_combine_dev(flint_attn *a, int32_t layer, int32_t n, int32_t 
     Layer &L = a->layer(layer);
     if (n <= 0 || n_parts <= 0) throw std::runtime_error("bad combine shape");
     if (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16) throw std::runtime_error("bad out dtype");
-    CombineParams cp{partials_dev, L.sinks, out_dev, n, n_parts, out_dtype};
+    CombineParams cp{};
+    cp.partials = partials_dev; cp.sinks = L.sinks; cp.out = out_dev;
+    cp.n = n; cp.n_parts = n_parts; cp.out_dtype = out_dtype;
+    cp.part_stride = n * kNHead * kPartialDim;
     CK(launch_combine(cp, cudaStream_t(cuda_stream)));
     a->launches++;
     return 0;
@@ -534,6 +650,10 @@ int32_t flint_attn_check(flint_attn *a, char *err, int32_t err_len) {
     int flag = 0;
     CK(prefill_error_flag(a->pf, &flag));
     if (flag) throw std::runtime_error("prefill kernel reported device error " + std::to_string(flag));
+    if (a->xchg) {
+        CK(cudaMemcpy(&flag, a->xchg + kMaxPeers * sizeof(uint32_t), sizeof(int), cudaMemcpyDeviceToHost));
+        if (flag) throw std::runtime_error("the wait for a peer's partial records ran out (exchange error " + std::to_string(flag) + ")");
+    }
     return 0;
     API_CATCH(-1)
 }

@@ -103,6 +103,33 @@ int32_t flint_attn_decode_partial_dev(flint_attn *a, int32_t layer, int32_t n, c
 int32_t flint_attn_combine_dev(flint_attn *a, int32_t layer, int32_t n, int32_t n_parts, const float *partials_dev,
                                void *out_dev, int32_t out_dtype, void *cuda_stream, char *err, int32_t err_len);
 
+/* ---- KV-range sharded decode with the exchange inside the kernels (GPUs of one node, peer access) ----
+ * No counterpart in the reference (one device).  Instead of decode_partial + an all-gather by a library + combine,
+ * the decode kernel itself stores each finished record into a gather buffer in EVERY rank's memory (plain peer
+ * stores over NVLink) and the last group of the launch publishes the step number in every rank's flag word; the
+ * combine kernel waits (bounded, about a second) on its own rank's flag words and merges records that are by then
+ * local.  Per step every rank calls post, then combine, on one stream; records are double-buffered by step parity.
+ *
+ *   xchg_create        allocates this rank's buffer for batches up to n_max tokens and returns its CUDA IPC handle
+ *                      (FLINT_ATTN_IPC_HANDLE_BYTES bytes; ipc_handle_out may be NULL inside one process).
+ *   xchg_connect       opens the other ranks' buffers: ipc_handles = kv_ranks handles in rank order (own one ignored).
+ *   xchg_connect_local same for handles that live in ONE process: peer_bases[r] = flint_attn_xchg_base(handle r).
+ *   decode_xchg_post   = decode_partial_dev, records to every rank.  Full layers only.
+ *   combine_xchg       = combine_dev over the records of the step just posted.  A wait that ran out makes the next
+ *                      flint_attn_check fail; the output of that call is then undefined.
+ * Kernels of two ranks that share ONE GPU must not wait on one another: there, post for every rank before any
+ * combine. */
+enum { FLINT_ATTN_IPC_HANDLE_BYTES = 64 };
+int32_t flint_attn_xchg_create(flint_attn *a, int32_t n_max, void *ipc_handle_out, char *err, int32_t err_len);
+int32_t flint_attn_xchg_connect(flint_attn *a, const void *ipc_handles, char *err, int32_t err_len);
+void *flint_attn_xchg_base(flint_attn *a);
+int32_t flint_attn_xchg_connect_local(flint_attn *a, void *const *peer_bases, char *err, int32_t err_len);
+int32_t flint_attn_decode_xchg_post_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs,
+                                        const void *qkv_dev, int32_t qkv_dtype, void *cuda_stream, char *err,
+                                        int32_t err_len);
+int32_t flint_attn_combine_xchg_dev(flint_attn *a, int32_t layer, int32_t n, void *out_dev, int32_t out_dtype,
+                                    void *cuda_stream, char *err, int32_t err_len);
+
 /* ---- prefill: n_tok tokens of one sequence from its current position -----------------------------
  * Replaces the chunk loop k_qk_prefill + k_attn_prefill (src/engine.mm:1080-1104, src/metal/prefill.metal:100-266):
  * norm(+RoPE at p0+t), K/V to the cache (ring slot (p0+t) & 1023 on SWA layers), causal + window + sink flash

@@ -230,3 +230,84 @@ def test_errors_do_not_cross_the_boundary(fa, fo):
         assert h.truncate(0, 65) == -1 and h.truncate(0, -1) == -1 and h.truncate(0, 10) == 0 and h.pos(0) == 10
     with pytest.raises(fa.FlintAttnError):
         fa.Attn([True], [True], 1, 128, device=99)
+
+
+def _sharded_pair(fa, w, n_ctx, k, v, pos):
+    """Two KV-range shards of one sequence as two handles on this GPU, exchange buffers connected in-process."""
+    handles = [_open(fa, ["full_rope"], 1, n_ctx, kv_rank=r, kv_ranks=2) for r in range(2)]
+    for r, h in enumerate(handles):
+        h.set_layer(0, *w)
+        lo, n = r * (n_ctx // 2), h.n_slots(0)
+        hi = min(pos, lo + n)
+        if hi > lo:
+            h.write_kv(0, 0, 0, k[lo:hi].transpose(1, 0, 2).copy(), v[lo:hi].transpose(1, 0, 2).copy())
+        h.set_pos(0, pos)
+        h.xchg_create(1)
+    bases = [h.xchg_base() for h in handles]
+    for h in handles:
+        h.xchg_connect_local(bases)
+    return handles
+
+
+def test_kv_sharded_exchange_through_peer_buffers(fa, fo):
+    """The decode kernel stores its records into every rank's gather buffer and publishes a step flag; the combine
+    kernel waits on the flags and merges.  Both ranks live on this one GPU here, so every rank posts before any
+    rank combines (a waiting kernel never runs ahead of its producer).  Three steps in a row cover both record
+    buffers and their reuse; every rank's output equals the unsharded decode."""
+    import torch
+
+    seed, n_ctx, P, steps = 11, 6000, 2998, 4  # the token's owner changes from shard 0 to shard 1 at position 3000
+    w = fo.layer_weights(seed, 0)
+    k, v = synth_cache_f16(seed, 0, 0, P)
+    rows = fo.raw_qkv(seed, 0, P, steps)
+    refs = np.empty((steps, 4096), np.float32)
+    with _open(fa, ["full_rope"], 1, n_ctx) as h0:
+        h0.set_layer(0, *w)
+        h0.write_kv(0, 0, 0, to_slot_layout(k, n_ctx, False), to_slot_layout(v, n_ctx, False))
+        h0.set_pos(0, P)
+        for s in range(steps):
+            h0.decode(0, [0], rows[s], fa.F32, refs[s:s + 1], fa.F32)
+            h0.advance([0])
+    handles = _sharded_pair(fa, w, n_ctx, k, v, P)
+    try:
+        with pytest.raises(fa.FlintAttnError, match="nothing was posted"):
+            handles[0].combine_xchg_dev(0, 1, torch.empty(1, 4096, device="cuda"), fa.F32)
+        outs = torch.zeros(2, steps, 4096, device="cuda")
+        for s in range(steps):
+            q_dev = torch.from_numpy(rows[s:s + 1]).cuda()
+            for h in handles:
+                h.decode_xchg_post_dev(0, [0], q_dev, fa.F32)
+            for r, h in enumerate(handles):
+                h.combine_xchg_dev(0, 1, outs[r, s:s + 1], fa.F32)
+                h.advance([0])
+        torch.cuda.synchronize()
+        for h in handles:
+            h.check()
+        got = outs.cpu().numpy()
+        assert np.abs(got[0] - refs).max() < 2e-5 and np.abs(got[1] - refs).max() < 2e-5
+    finally:
+        for h in handles:
+            h.close()
+
+
+def test_exchange_wait_is_bounded(fa, fo):
+    """A rank whose peer never posts: the combine kernel gives up after about a second, records the fact, and the
+    context stays usable (the next check reports it; nothing hangs or faults)."""
+    import torch
+
+    seed, n_ctx, P = 12, 2048, 300
+    w = fo.layer_weights(seed, 0)
+    k, v = synth_cache_f16(seed, 0, 0, P)
+    handles = _sharded_pair(fa, w, n_ctx, k, v, P)
+    try:
+        q_dev = torch.from_numpy(fo.raw_qkv(seed, 0, P, 1)).cuda()
+        out = torch.zeros(1, 4096, device="cuda")
+        handles[0].decode_xchg_post_dev(0, [0], q_dev, fa.F32)  # rank 1 stays silent
+        handles[0].combine_xchg_dev(0, 1, out, fa.F32)
+        with pytest.raises(fa.FlintAttnError, match="ran out"):
+            handles[0].check()
+        torch.cuda.synchronize()
+        assert float((out + 1).sum().item()) == 4096.0  # the device still answers; the output was left alone
+    finally:
+        for h in handles:
+            h.close()
