@@ -33,6 +33,25 @@ constexpr int kTileBytes = kTileKeys * kRowBytes;   // 16 KiB per K or V tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// Debug timeline (only with -DFLINT_DEC_TRACE): per CTA, clock64 at up to 12 points plus %globaltimer at entry/exit.
+#ifdef FLINT_DEC_TRACE
+constexpr int kTraceCtas = 1024, kTraceSlots = 16;
+__device__ long long g_dec_trace[kTraceCtas * kTraceSlots];
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+#define DEC_TRACE(slot)                                                                              \
+    do {                                                                                             \
+        if (threadIdx.x == 0 && blockIdx.x < kTraceCtas) {                                           \
+            g_dec_trace[blockIdx.x * kTraceSlots + (slot)] = (slot) >= 12 ? global_ns() : clock64(); \
+        }                                                                                            \
+    } while (0)
+#else
+#define DEC_TRACE(slot) do { } while (0)
+#endif
+
 struct __align__(16) DecSmem {
     unsigned char k[kStages][kTileBytes];
     unsigned char v[kStages][kTileBytes];
@@ -41,6 +60,8 @@ struct __align__(16) DecSmem {
     __half vnew[kHeadDim];
     float red_m[kWarps][kGqa];
     float red_l[kWarps][kGqa];
+    float rope_cos[kHeadDim / 2];  // cos / sin of pos * inv_freq[i], shared by the 8 query heads and the new key
+    float rope_sin[kHeadDim / 2];
     int is_last;
 };
 // The per-warp output accumulators are merged through the (by then idle) K tiles.
@@ -55,26 +76,22 @@ __device__ __forceinline__ float4 load_row4(const void *base, int dtype, size_t 
 }
 
 // One 128-wide head row spread over a warp, lane owning dims 4*lane..4*lane+3: RMSNorm with weight, then NEOX RoPE
-// pairing dim i with i+64, i.e. lane with lane^16 (same arithmetic as src/ref/ref_model.cpp:45-61).
-__device__ __forceinline__ float4 norm_rope(float4 v, const float *w, const float *inv_freq, int lane, int pos,
-                                            bool rope) {
+// pairing dim i with i+64, i.e. lane with lane^16 (same arithmetic as src/ref/ref_model.cpp:45-61).  cs/sn hold
+// cos/sin of pos * inv_freq[4*(lane&15) .. +3], computed once per CTA.
+__device__ __forceinline__ float4 norm_rope(float4 v, float4 wv, float4 cs, float4 sn, int lane, bool rope) {
     const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
     const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps);
-    const float4 wv = reinterpret_cast<const float4 *>(w)[lane];
     v.x = v.x * scale * wv.x;
     v.y = v.y * scale * wv.y;
     v.z = v.z * scale * wv.z;
     v.w = v.w * scale * wv.w;
     if (!rope) return v;
-    float x[4] = {v.x, v.y, v.z, v.w}, out[4];
-    const float4 fr = reinterpret_cast<const float4 *>(inv_freq)[lane & 15];
-    const float freq[4] = {fr.x, fr.y, fr.z, fr.w};
+    const float x[4] = {v.x, v.y, v.z, v.w}, c[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+    float out[4];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const float partner = __shfl_xor_sync(0xffffffffu, x[j], 16);
-        float s, c;
-        sincosf(float(pos) * freq[j], &s, &c);
-        out[j] = lane < 16 ? x[j] * c - partner * s : partner * s + x[j] * c;
+        out[j] = lane < 16 ? x[j] * c[j] - partner * sv[j] : partner * sv[j] + x[j] * c[j];
     }
     return make_float4(out[0], out[1], out[2], out[3]);
 }
@@ -87,6 +104,23 @@ __device__ __forceinline__ void store_half4(__half *dst, float4 v) {
 __device__ __forceinline__ void store_out(void *out, int dtype, size_t idx, float v) {
     if (dtype == kDtypeF32) static_cast<float *>(out)[idx] = v;
     else static_cast<__nv_bfloat16 *>(out)[idx] = __float2bfloat16_rn(v);
+}
+
+// 8 consecutive outputs of one head as one or two 16-byte stores.
+__device__ __forceinline__ void store_out8(void *out, int dtype, size_t idx, const float (&v)[8]) {
+    if (dtype == kDtypeF32) {
+        float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(out) + idx);
+        dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+        dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t *>(&b);
+        }
+        *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(out) + idx) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
 }
 
 struct Merged {
@@ -106,9 +140,10 @@ __device__ __forceinline__ float *record_target(const DecParams &p, int t, int t
 // publishes the step number in every peer's flag word for this rank (release at system scope).
 __device__ __forceinline__ void publish_group(const DecParams &p, int tid) {
     if (p.mode != 2) return;
-    __threadfence_system();
     __syncthreads();
-    if (tid == 0 && atomicAdd(p.groups_done, 1) == p.n_groups - 1) {
+    if (tid != 0) return;
+    __threadfence_system();  // cumulative over the CTA's stores, which the barrier ordered before it
+    if (atomicAdd(p.groups_done, 1) == p.n_groups - 1) {
         *p.groups_done = 0;
         __threadfence_system();
         for (int t = 0; t < p.n_peers; t++)
@@ -154,6 +189,12 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     const int j0 = it.j0, j1 = it.j1;
     const int j_end = j1 + (it.fold ? 1 : 0);  // the new token sits right after the cached range of a fold item
     const int n_tiles = (j_end - j0 + kTileKeys - 1) / kTileKeys;
+    DEC_TRACE(12);
+    DEC_TRACE(0);
+    // layout of the merge steps at the end: 16 threads per head, 8 dims per thread; the head's sink is fetched now
+    const int mh = tid >> 4, md = (tid & 15) * 8;
+    const int head = it.kvh * kGqa + mh;
+    const float sink = p.sinks[head];
 
     const __half *kbase = p.k_cache + size_t(it.seq) * p.seq_stride + size_t(it.kvh) * p.n_slots * kHeadDim;
     const __half *vbase = p.v_cache + size_t(it.seq) * p.seq_stride + size_t(it.kvh) * p.n_slots * kHeadDim;
@@ -182,35 +223,52 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         if (t < n_tiles) load_tile(t);
         cp_async_commit();
     }
+    DEC_TRACE(1);
 
     // ---- prologue: q heads of the group (and the new token's k, v) -> shared memory --------------------------
+    // Every global load is issued first; the 64 rotation angles are evaluated once per CTA while they are in flight.
     {
         const size_t row0 = size_t(it.tok) * kQkvDim;
         const float qscale = rsqrtf(float(kHeadDim)) * kLog2e;  // softmax runs in base 2
+        const bool rope = p.has_rope != 0;
+        const bool fold_k = it.fold && warp == 0, fold_v = it.fold && warp == 1;
+        float4 q[2];
+#pragma unroll
+        for (int i = 0; i < 2; i++)
+            q[i] = load_row4(p.qkv, p.qkv_dtype, row0 + size_t(it.kvh * kGqa + warp * 2 + i) * kHeadDim, lane);
+        float4 kv_new = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (fold_k) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + size_t(it.kvh) * kHeadDim, lane);
+        if (fold_v) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + kKvDim + size_t(it.kvh) * kHeadDim, lane);
+        const float4 wq = reinterpret_cast<const float4 *>(p.q_norm)[lane];
+        float4 wk = wq;
+        if (fold_k) wk = reinterpret_cast<const float4 *>(p.k_norm)[lane];
+        if (rope && tid < kHeadDim / 2) {
+            float sn, cs;
+            sincosf(float(it.pos) * p.inv_freq[tid], &sn, &cs);
+            sm.rope_cos[tid] = cs;
+            sm.rope_sin[tid] = sn;
+        }
+        __syncthreads();
+        float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (rope) {
+            cs = reinterpret_cast<const float4 *>(sm.rope_cos)[lane & 15];
+            sn = reinterpret_cast<const float4 *>(sm.rope_sin)[lane & 15];
+        }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-            const int hl = warp * 2 + i;  // head within the group
-            float4 q = load_row4(p.qkv, p.qkv_dtype, row0 + size_t(it.kvh * kGqa + hl) * kHeadDim, lane);
-            q = norm_rope(q, p.q_norm, p.inv_freq, lane, it.pos, p.has_rope != 0);
-            q.x *= qscale; q.y *= qscale; q.z *= qscale; q.w *= qscale;
-            store_half4(&sm.q[hl][4 * lane], q);
+            float4 r = norm_rope(q[i], wq, cs, sn, lane, rope);
+            r.x *= qscale; r.y *= qscale; r.z *= qscale; r.w *= qscale;
+            store_half4(&sm.q[warp * 2 + i][4 * lane], r);
         }
-        if (it.fold) {
-            if (warp == 0) {
-                float4 k = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + size_t(it.kvh) * kHeadDim, lane);
-                k = norm_rope(k, p.k_norm, p.inv_freq, lane, it.pos, p.has_rope != 0);
-                store_half4(&sm.knew[4 * lane], k);
-                const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
-                store_half4(const_cast<__half *>(kbase) + size_t(slot) * kHeadDim + 4 * lane, k);
-            } else if (warp == 1) {
-                const float4 v = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + kKvDim + size_t(it.kvh) * kHeadDim, lane);
-                store_half4(&sm.vnew[4 * lane], v);
-                const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
-                store_half4(const_cast<__half *>(vbase) + size_t(slot) * kHeadDim + 4 * lane, v);
-            }
+        if (fold_k || fold_v) {
+            if (fold_k) kv_new = norm_rope(kv_new, wk, cs, sn, lane, rope);
+            store_half4(fold_k ? &sm.knew[4 * lane] : &sm.vnew[4 * lane], kv_new);
+            const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
+            store_half4(const_cast<__half *>(fold_k ? kbase : vbase) + size_t(slot) * kHeadDim + 4 * lane, kv_new);
         }
     }
     __syncthreads();
+    DEC_TRACE(2);
 
     // B fragments of Q^T for the 8 k-steps: b0 = Q[head g][16k + 2t, +1], b1 = Q[head g][16k + 8 + 2t, +1]
     uint32_t bq[8][2];
@@ -297,6 +355,7 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with the tiles: the K tiles become the merge buffer
+    DEC_TRACE(3);
 
     // ---- merge the four warps --------------------------------------------------------------------------------
 #pragma unroll
@@ -319,45 +378,54 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     }
     __syncthreads();
 
-    const int d = tid;  // this thread owns one of the 128 output dims for all 8 heads
+    // From here on a thread owns 8 dims of one head (16 threads per head), so each step is a couple of wide,
+    // independent loads per thread instead of a loop over heads.
     const bool direct = it.n_split == 1;
-    float *rec_base = direct ? nullptr : p.scratch + (size_t(it.part0) + it.split) * kGqa * kRecStride;
-#pragma unroll 1
-    for (int h = 0; h < kGqa; h++) {
+    {
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kWarps; w++) M = fmaxf(M, sm.red_m[w][h]);
-        float L = 0.f, A = 0.f;
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, sm.red_m[w][mh]);
+        float L = 0.f, A[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) A[j] = 0.f;
 #pragma unroll
         for (int w = 0; w < kWarps; w++) {
-            const float lw = sm.red_l[w][h];
-            if (lw == 0.f) continue;  // a warp that saw no key: m = -inf, skip (fused.metal:314)
-            const float c = fast_exp2(sm.red_m[w][h] - M);
+            const float lw = sm.red_l[w][mh];
+            // a warp that saw no key has m = -inf, l = 0 and contributes nothing (fused.metal:314)
+            const float c = lw == 0.f ? 0.f : fast_exp2(sm.red_m[w][mh] - M);
+            const float4 x = *reinterpret_cast<const float4 *>(obuf + (size_t(w) * kGqa + mh) * kHeadDim + md);
+            const float4 y = *reinterpret_cast<const float4 *>(obuf + (size_t(w) * kGqa + mh) * kHeadDim + md + 4);
             L += lw * c;
-            A += obuf[(size_t(w) * kGqa + h) * kHeadDim + d] * c;
+            A[0] += x.x * c; A[1] += x.y * c; A[2] += x.z * c; A[3] += x.w * c;
+            A[4] += y.x * c; A[5] += y.y * c; A[6] += y.z * c; A[7] += y.w * c;
         }
-        const int head = it.kvh * kGqa + h;
         if (direct && p.mode == 0) {
             // single split: fold the sink here (fused.metal:319-322), all in base 2
-            const float sink2 = p.sinks[head] * kLog2e;
+            const float sink2 = sink * kLog2e;
             const float Mf = fmaxf(M, sink2), cs = fast_exp2(M - Mf);
-            store_out(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + d,
-                      A * cs / (L * cs + fast_exp2(sink2 - Mf)));
+            const float inv = cs / (L * cs + fast_exp2(sink2 - Mf));
+#pragma unroll
+            for (int j = 0; j < 8; j++) A[j] *= inv;
+            store_out8(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + md, A);
         } else if (direct) {
             // this device's only record for the token: {acc[128], m, l}, m in natural-log units (fused.metal:324-327)
             for (int t = 0; t < n_record_targets(p); t++) {
-                float *rec = record_target(p, t, it.tok, head);
-                rec[d] = A;
-                if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
+                float *rec = record_target(p, t, it.tok, head);  // 130-float records: 8-byte aligned only
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) *reinterpret_cast<float2 *>(rec + md + j) = make_float2(A[j], A[j + 1]);
+                if (md == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
             }
         } else {
-            float *rec = rec_base + size_t(h) * kRecStride;
-            rec[d] = A;
-            if (d == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
+            float *rec = p.scratch + ((size_t(it.part0) + it.split) * kGqa + mh) * kRecStride;
+            *reinterpret_cast<float4 *>(rec + md) = make_float4(A[0], A[1], A[2], A[3]);
+            *reinterpret_cast<float4 *>(rec + md + 4) = make_float4(A[4], A[5], A[6], A[7]);
+            if (md == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
         }
     }
+    DEC_TRACE(4);
     if (direct) {
         publish_group(p, tid);
+        DEC_TRACE(13);
         return;
     }
 
@@ -366,17 +434,22 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     // each run of 16 splits folds those records into one; the last of those to finish folds the runs and the sink.
     const int sub = it.split / kMergeFan, n_sub = (it.n_split + kMergeFan - 1) / kMergeFan;
     const int sub_size = min(kMergeFan, it.n_split - sub * kMergeFan);
-    __threadfence();
+    // The CTA's record stores are ordered before thread 0's fence by the barrier, and the fence is cumulative, so
+    // one thread publishes for all; on the reading side its second fence plus the barrier cover the other threads,
+    // which read the records past L1 (ld.cg).
     __syncthreads();
-    if (tid == 0) sm.is_last = (atomicAdd(&p.tickets[it.sub0 + sub], 1) == sub_size - 1);
+    if (tid == 0) {
+        __threadfence();
+        const bool last = atomicAdd(&p.tickets[it.sub0 + sub], 1) == sub_size - 1;
+        if (last) p.tickets[it.sub0 + sub] = 0;  // ready for the next launch
+        __threadfence();
+        sm.is_last = last;
+    }
     __syncthreads();
+    DEC_TRACE(5);
+    DEC_TRACE(13);
     if (!sm.is_last) return;
-    __threadfence();
-    if (tid == 0) p.tickets[it.sub0 + sub] = 0;  // ready for the next launch
 
-    const int mh = tid >> 4, md = (tid & 15) * 8;  // merge layout: 16 threads per head, 8 dims per thread
-    const int head = it.kvh * kGqa + mh;
-    const float sink = p.sinks[head];
     const float *lvl1 = p.scratch + ((size_t(it.part0) + sub * kMergeFan) * kGqa + mh) * kRecStride;
     Merged r;
     if (n_sub == 1) {
@@ -387,31 +460,25 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         *reinterpret_cast<float4 *>(rec2 + md) = make_float4(r.a[0], r.a[1], r.a[2], r.a[3]);
         *reinterpret_cast<float4 *>(rec2 + md + 4) = make_float4(r.a[4], r.a[5], r.a[6], r.a[7]);
         if (md == 0) { rec2[kHeadDim] = r.M; rec2[kHeadDim + 1] = r.L; }
-        __threadfence();
         __syncthreads();
-        if (tid == 0) sm.is_last = (atomicAdd(&p.tickets2[it.group], 1) == n_sub - 1);
+        if (tid == 0) {
+            __threadfence();
+            const bool last = atomicAdd(&p.tickets2[it.group], 1) == n_sub - 1;
+            if (last) p.tickets2[it.group] = 0;
+            __threadfence();
+            sm.is_last = last;
+        }
         __syncthreads();
+        DEC_TRACE(6);
+        DEC_TRACE(13);
         if (!sm.is_last) return;
-        __threadfence();
-        if (tid == 0) p.tickets2[it.group] = 0;
         r = merge_records(p.scratch2 + (size_t(it.sub0) * kGqa + mh) * kRecStride, n_sub, md, p.mode == 0, sink);
     }
     if (p.mode == 0) {
         const float inv = 1.0f / r.L;
-        const size_t o = size_t(it.tok) * kQDim + head * kHeadDim + md;
-        if (p.out_dtype == kDtypeF32) {
-            float4 *dst = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + o);
-            dst[0] = make_float4(r.a[0] * inv, r.a[1] * inv, r.a[2] * inv, r.a[3] * inv);
-            dst[1] = make_float4(r.a[4] * inv, r.a[5] * inv, r.a[6] * inv, r.a[7] * inv);
-        } else {
-            uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const __nv_bfloat162 b = __floats2bfloat162_rn(r.a[2 * j] * inv, r.a[2 * j + 1] * inv);
-                w[j] = *reinterpret_cast<const uint32_t *>(&b);
-            }
-            *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) + o) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        for (int j = 0; j < 8; j++) r.a[j] *= inv;
+        store_out8(p.out, p.out_dtype, size_t(it.tok) * kQDim + head * kHeadDim + md, r.a);
     } else {
         for (int t = 0; t < n_record_targets(p); t++) {
             float *rec = record_target(p, t, it.tok, head);  // 130-float public record
@@ -421,6 +488,8 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         }
         publish_group(p, tid);
     }
+    DEC_TRACE(7);
+    DEC_TRACE(13);
 }
 
 // The work list either sits in device memory (any length) or, when it is short enough, travels in the kernel's
@@ -511,5 +580,17 @@ cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream) {
     k_combine_parts<<<p.n * kNHead, kHeadDim, 0, stream>>>(p);
     return cudaGetLastError();
 }
+
+#ifdef FLINT_DEC_TRACE
+extern "C" int flint_dec_trace_read(long long *out, int clear) {
+    if (cudaMemcpyFromSymbol(out, g_dec_trace, sizeof(long long) * kTraceCtas * kTraceSlots) != cudaSuccess) return -1;
+    if (clear) {
+        void *ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_dec_trace) != cudaSuccess) return -1;
+        cudaMemset(ptr, 0, sizeof(long long) * kTraceCtas * kTraceSlots);
+    }
+    return 0;
+}
+#endif
 
 }  // namespace flint
