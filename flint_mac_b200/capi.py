@@ -91,9 +91,20 @@ def load_library() -> C.CDLL:
     return _lib
 
 
-def _i32(xs: Sequence[int]):
-    arr = (C.c_int32 * len(xs))(*[int(x) for x in xs])
-    return arr
+def _i32(xs):
+    """int32 C array for a sequence of ints.  A ctypes int32 array (see i32_array) passes through untouched, so a
+    caller that decodes the same batch every step converts its sequence list once."""
+    if isinstance(xs, C.Array) and xs._type_ is C.c_int32:
+        return xs
+    if isinstance(xs, np.ndarray):
+        xs = np.ascontiguousarray(xs, np.int32)
+        return (C.c_int32 * xs.size).from_buffer_copy(xs)
+    return (C.c_int32 * len(xs))(*xs)
+
+
+def i32_array(xs):
+    """Convert once, pass many times: the result is accepted wherever a list of sequence indices is."""
+    return _i32(xs)
 
 
 def _ptr(x) -> int:
@@ -142,6 +153,7 @@ class Attn:
     def __init__(self, layer_is_swa: Sequence[bool], layer_has_rope: Sequence[bool], max_seqs: int, n_ctx: int,
                  device: int = 0, kv_rank: int = 0, kv_ranks: int = 1):
         self._lib = load_library()
+        self._err = C.create_string_buffer(ERR_LEN)
         self.n_layers = len(layer_is_swa)
         swa, rope = _i32([int(b) for b in layer_is_swa]), _i32([int(b) for b in layer_has_rope])
         cfg = _Config(device, self.n_layers, swa, rope, max_seqs, n_ctx, kv_rank, kv_ranks)
@@ -167,7 +179,7 @@ class Attn:
         self.close()
 
     def _call(self, name, *args):
-        err = C.create_string_buffer(ERR_LEN)
+        err = self._err  # one buffer per handle (single owner, not thread-safe): nothing is allocated per call
         r = getattr(self._lib, name)(self._h, *args, err, ERR_LEN)
         if r != 0:
             raise FlintAttnError(err.value.decode(errors="replace"))

@@ -151,29 +151,46 @@ __device__ __forceinline__ void publish_group(const DecParams &p, int tid) {
     }
 }
 
-// Fold n partial records of one head (fused.metal:332-350): M = max m_s (and the sink), L = sum l_s e^(m_s - M)
-// (+ e^(sink - M)), a = sum acc_s e^(m_s - M).  `rec` points at record 0 of this thread's head; consecutive records
-// of the same head are kGqa * kRecStride floats apart.  The thread owns dims [d0, d0 + 8).  Loads are independent
-// across records, so the unrolled loops keep many of them in flight.
+// Fold n partial records of one head (fused.metal:332-350) into the running state (M, L, a): M = max m_s,
+// L = sum l_s e^(m_s - M), a = sum acc_s e^(m_s - M); the sink enters as a record with m = sink, l = 1, acc = 0.
+// `rec` points at record 0 of this thread's head; consecutive records of the same head are kGqa * kRecStride floats
+// apart.  The thread owns dims [d0, d0 + 8).  Eight records per trip: their 24 loads are in flight together (a trip costs about a microsecond), and
+// the loop stays small -- this code runs once per group, from a cold instruction cache, so its size is its cost.
 __device__ __forceinline__ Merged merge_records(const float *rec, int n, int d0, bool with_sink, float sink) {
     constexpr int kStep = kGqa * kRecStride;
+    constexpr int kTrip = 8;  // records per round trip to L2
     Merged r;
-    float M = with_sink ? sink : -INFINITY;
-#pragma unroll 8
-    for (int s = 0; s < n; s++) M = fmaxf(M, __ldcg(rec + size_t(s) * kStep + kHeadDim));
-    float L = with_sink ? __expf(sink - M) : 0.f;
+    float M = with_sink ? sink : -INFINITY, L = with_sink ? 1.f : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; j++) r.a[j] = 0.f;
-#pragma unroll 8
-    for (int s = 0; s < n; s++) {
-        const float *q = rec + size_t(s) * kStep;
-        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(q + kHeadDim));
-        const float4 x = __ldcg(reinterpret_cast<const float4 *>(q + d0));
-        const float4 y = __ldcg(reinterpret_cast<const float4 *>(q + d0 + 4));
-        const float c = ml.y == 0.f ? 0.f : __expf(ml.x - M);  // an empty part has m = -inf, l = 0 (fused.metal:344)
-        L += ml.y * c;
-        r.a[0] += x.x * c; r.a[1] += x.y * c; r.a[2] += x.z * c; r.a[3] += x.w * c;
-        r.a[4] += y.x * c; r.a[5] += y.y * c; r.a[6] += y.z * c; r.a[7] += y.w * c;
+#pragma unroll 1
+    for (int s0 = 0; s0 < n; s0 += kTrip) {
+        float2 ml[kTrip];
+        float4 x[kTrip], y[kTrip];
+#pragma unroll
+        for (int i = 0; i < kTrip; i++) {
+            const float *q = rec + size_t(min(s0 + i, n - 1)) * kStep;  // past the end: re-read the last one, unused
+            ml[i] = __ldcg(reinterpret_cast<const float2 *>(q + kHeadDim));
+            x[i] = __ldcg(reinterpret_cast<const float4 *>(q + d0));
+            y[i] = __ldcg(reinterpret_cast<const float4 *>(q + d0 + 4));
+            if (s0 + i >= n) ml[i] = make_float2(-INFINITY, 0.f);
+        }
+        float cm = M;
+#pragma unroll
+        for (int i = 0; i < kTrip; i++) cm = fmaxf(cm, ml[i].x);
+        const float keep = M == -INFINITY ? 0.f : __expf(M - cm);
+        L *= keep;
+#pragma unroll
+        for (int j = 0; j < 8; j++) r.a[j] *= keep;
+        M = cm;
+#pragma unroll
+        for (int i = 0; i < kTrip; i++) {
+            // an empty part has m = -inf, l = 0 (fused.metal:344)
+            const float c = ml[i].y == 0.f ? 0.f : __expf(ml[i].x - M);
+            L += ml[i].y * c;
+            r.a[0] += x[i].x * c; r.a[1] += x[i].y * c; r.a[2] += x[i].z * c; r.a[3] += x[i].w * c;
+            r.a[4] += y[i].x * c; r.a[5] += y[i].y * c; r.a[6] += y[i].z * c; r.a[7] += y[i].w * c;
+        }
     }
     r.M = M;
     r.L = L;
@@ -217,7 +234,26 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         }
     };
 
-    // Start the first tiles before the query prologue so their latency overlaps it.
+
+    // ---- prologue: q heads of the group (and the new token's k, v) -> shared memory --------------------------
+    // The row loads go out first, then the first K/V tiles, so that neither waits behind the other's latency; the 64
+    // rotation angles are evaluated once per CTA while all of them are in flight.
+    const size_t row0 = size_t(it.tok) * kQkvDim;
+    const bool rope = p.has_rope != 0;
+    const bool fold_k = it.fold && warp == 0, fold_v = it.fold && warp == 1;
+    float4 q[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+        q[i] = load_row4(p.qkv, p.qkv_dtype, row0 + size_t(it.kvh * kGqa + warp * 2 + i) * kHeadDim, lane);
+    float4 kv_new = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (fold_k) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + size_t(it.kvh) * kHeadDim, lane);
+    if (fold_v) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + kKvDim + size_t(it.kvh) * kHeadDim, lane);
+    const float4 wq = reinterpret_cast<const float4 *>(p.q_norm)[lane];
+    float4 wk = wq;
+    if (fold_k) wk = reinterpret_cast<const float4 *>(p.k_norm)[lane];
+    float freq = 0.f;
+    if (rope && tid < kHeadDim / 2) freq = p.inv_freq[tid];
+
 #pragma unroll
     for (int t = 0; t < kStages - 1; t++) {
         if (t < n_tiles) load_tile(t);
@@ -225,26 +261,11 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     }
     DEC_TRACE(1);
 
-    // ---- prologue: q heads of the group (and the new token's k, v) -> shared memory --------------------------
-    // Every global load is issued first; the 64 rotation angles are evaluated once per CTA while they are in flight.
     {
-        const size_t row0 = size_t(it.tok) * kQkvDim;
         const float qscale = rsqrtf(float(kHeadDim)) * kLog2e;  // softmax runs in base 2
-        const bool rope = p.has_rope != 0;
-        const bool fold_k = it.fold && warp == 0, fold_v = it.fold && warp == 1;
-        float4 q[2];
-#pragma unroll
-        for (int i = 0; i < 2; i++)
-            q[i] = load_row4(p.qkv, p.qkv_dtype, row0 + size_t(it.kvh * kGqa + warp * 2 + i) * kHeadDim, lane);
-        float4 kv_new = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (fold_k) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + size_t(it.kvh) * kHeadDim, lane);
-        if (fold_v) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + kKvDim + size_t(it.kvh) * kHeadDim, lane);
-        const float4 wq = reinterpret_cast<const float4 *>(p.q_norm)[lane];
-        float4 wk = wq;
-        if (fold_k) wk = reinterpret_cast<const float4 *>(p.k_norm)[lane];
         if (rope && tid < kHeadDim / 2) {
             float sn, cs;
-            sincosf(float(it.pos) * p.inv_freq[tid], &sn, &cs);
+            sincosf(float(it.pos) * freq, &sn, &cs);
             sm.rope_cos[tid] = cs;
             sm.rope_sin[tid] = sn;
         }
@@ -441,8 +462,10 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     if (tid == 0) {
         __threadfence();
         const bool last = atomicAdd(&p.tickets[it.sub0 + sub], 1) == sub_size - 1;
-        if (last) p.tickets[it.sub0 + sub] = 0;  // ready for the next launch
-        __threadfence();
+        if (last) {
+            p.tickets[it.sub0 + sub] = 0;  // ready for the next launch
+            __threadfence();
+        }
         sm.is_last = last;
     }
     __syncthreads();
@@ -450,12 +473,14 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     DEC_TRACE(13);
     if (!sm.is_last) return;
 
-    const float *lvl1 = p.scratch + ((size_t(it.part0) + sub * kMergeFan) * kGqa + mh) * kRecStride;
+    // One copy of the merge code serves both levels (see merge_records on code size).
+    const float *src = p.scratch + ((size_t(it.part0) + sub * kMergeFan) * kGqa + mh) * kRecStride;
+    int n_src = sub_size;
+    bool final_level = n_sub == 1;
     Merged r;
-    if (n_sub == 1) {
-        r = merge_records(lvl1, sub_size, md, p.mode == 0, sink);
-    } else {
-        r = merge_records(lvl1, sub_size, md, false, 0.f);
+    for (;;) {
+        r = merge_records(src, n_src, md, final_level && p.mode == 0, sink);
+        if (final_level) break;
         float *rec2 = p.scratch2 + ((size_t(it.sub0) + sub) * kGqa + mh) * kRecStride;
         *reinterpret_cast<float4 *>(rec2 + md) = make_float4(r.a[0], r.a[1], r.a[2], r.a[3]);
         *reinterpret_cast<float4 *>(rec2 + md + 4) = make_float4(r.a[4], r.a[5], r.a[6], r.a[7]);
@@ -464,15 +489,19 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         if (tid == 0) {
             __threadfence();
             const bool last = atomicAdd(&p.tickets2[it.group], 1) == n_sub - 1;
-            if (last) p.tickets2[it.group] = 0;
-            __threadfence();
+            if (last) {
+                p.tickets2[it.group] = 0;
+                __threadfence();
+            }
             sm.is_last = last;
         }
         __syncthreads();
         DEC_TRACE(6);
         DEC_TRACE(13);
         if (!sm.is_last) return;
-        r = merge_records(p.scratch2 + (size_t(it.sub0) * kGqa + mh) * kRecStride, n_sub, md, p.mode == 0, sink);
+        src = p.scratch2 + (size_t(it.sub0) * kGqa + mh) * kRecStride;
+        n_src = n_sub;
+        final_level = true;
     }
     if (p.mode == 0) {
         const float inv = 1.0f / r.L;
@@ -494,9 +523,12 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
 
 // The work list either sits in device memory (any length) or, when it is short enough, travels in the kernel's
 // parameter space (large kernel parameters, up to 32 KiB): one wave on a 148-SM part is ~300 items of 48 bytes, so the
-// usual launch needs no host-to-device copy in front of it.
+// usual launch needs no host-to-device copy in front of it.  The parameter block is copied by the driver at every
+// launch, so the kernel comes in three capacities and a launch takes the smallest that fits (the smallest one stays
+// inside the classic 4 KiB parameter space).
+template <int kCap>
 struct DecItemsParam {
-    DecItem items[kMaxParamItems];
+    DecItem items[kCap];
 };
 
 __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
@@ -504,10 +536,23 @@ __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) 
     decode_item(p, it);
 }
 
+template <int kCap>
 __global__ void __launch_bounds__(kThreads, 2) k_decode_attn_p(const __grid_constant__ DecParams p,
-                                                               const __grid_constant__ DecItemsParam ip) {
+                                                               const __grid_constant__ DecItemsParam<kCap> ip) {
     const DecItem it = ip.items[blockIdx.x];
     decode_item(p, it);
+}
+
+constexpr int kCapSmall = 76, kCapMid = 256;
+static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kCapSmall>) <= 4096, "small variant fits 4 KiB of parameters");
+static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kMaxParamItems>) <= 32764, "largest variant fits the limit");
+
+template <int kCap>
+cudaError_t launch_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
+    static thread_local DecItemsParam<kCap> ip;  // copied into the launch by the runtime before this returns
+    memcpy(ip.items, host_items, sizeof(DecItem) * size_t(n_items));
+    k_decode_attn_p<kCap><<<n_items, kThreads, sizeof(DecSmem), stream>>>(p, ip);
+    return cudaGetLastError();
 }
 
 // Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.  With a
@@ -555,9 +600,14 @@ __global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams 
 }  // namespace
 
 cudaError_t decode_kernel_setup() {
-    cudaError_t e = cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(DecSmem)));
+    const int bytes = int(sizeof(DecSmem));
+    cudaError_t e = cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_decode_attn_p, cudaFuncAttributeMaxDynamicSharedMemorySize, int(sizeof(DecSmem)));
+    e = cudaFuncSetAttribute(k_decode_attn_p<kCapSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k_decode_attn_p<kCapMid>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(k_decode_attn_p<kMaxParamItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
 }
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) {
@@ -569,10 +619,9 @@ cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) 
 cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
     if (n_items > kMaxParamItems) return cudaErrorInvalidValue;
-    static thread_local DecItemsParam ip;  // copied into the launch by the runtime before this returns
-    memcpy(ip.items, host_items, sizeof(DecItem) * size_t(n_items));
-    k_decode_attn_p<<<n_items, kThreads, sizeof(DecSmem), stream>>>(p, ip);
-    return cudaGetLastError();
+    if (n_items <= kCapSmall) return launch_inline<kCapSmall>(p, host_items, n_items, stream);
+    if (n_items <= kCapMid) return launch_inline<kCapMid>(p, host_items, n_items, stream);
+    return launch_inline<kMaxParamItems>(p, host_items, n_items, stream);
 }
 
 cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream) {

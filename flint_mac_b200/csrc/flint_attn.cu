@@ -50,11 +50,20 @@ int round_up(int x, int m) { return (x + m - 1) / m * m; }
 // number of cached key rows of the launch divided by the slots; a (token, KV head) group gets round(keys / chunk)
 // splits (at least one), so a batch of equally long sequences is not cut in two just because it is a little longer
 // than the chunk.
+// The planner runs in front of every launch, so it allocates nothing once its buffers have grown, and it orders
+// the items through 64-bit (length, index) keys instead of moving 48-byte structs in a sort.
+struct PlanScratch {
+    std::vector<int> lo, hi;
+    std::vector<DecItem> gen;
+    std::vector<uint64_t> keys;
+};
+
 void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi, int target_items,
-                 std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs) {
-    items.clear();
+                 std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs, PlanScratch &ps) {
     long long total = 0;
-    std::vector<int> lo(n), hi(n);
+    ps.lo.resize(n);
+    ps.hi.resize(n);
+    int *lo = ps.lo.data(), *hi = ps.hi.data();
     for (int i = 0; i < n; i++) {
         const int kb = is_swa ? std::max(pos[i] - (kNSwa - 1), 0) : 0;  // src/metal/fused.metal:265
         lo[i] = std::min(std::max(kb, kv_lo), pos[i]);
@@ -67,6 +76,10 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
     n_groups = n * kNHeadKv;
     n_records = 0;
     n_subs = 0;
+    std::vector<DecItem> &gen = items;  // generated in place; reordered below only when needed
+    gen.clear();
+    bool sorted = true;  // already longest first?
+    int prev_len = INT32_MAX;
     for (int i = 0; i < n; i++) {
         const int nk = hi[i] - lo[i];
         const bool own_new = kv_lo <= pos[i] && pos[i] < kv_hi;
@@ -93,13 +106,22 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
                 it.part0 = part0;
                 it.group = i * kNHeadKv + kvh;
                 it.sub0 = sub0;
-                items.push_back(it);
+                const int len = it.j1 - it.j0;
+                sorted = sorted && len <= prev_len;
+                prev_len = len;
+                gen.push_back(it);
             }
         }
     }
     // longest first: the block scheduler hands CTAs out in order, which makes this a greedy LPT schedule
-    std::stable_sort(items.begin(), items.end(),
-                     [](const DecItem &a, const DecItem &b) { return a.j1 - a.j0 > b.j1 - b.j0; });
+    if (sorted) return;
+    const size_t m = items.size();
+    ps.keys.resize(m);
+    for (size_t i = 0; i < m; i++)  // ascending key = descending length, ties in generation order
+        ps.keys[i] = (uint64_t(uint32_t(INT32_MAX - (items[i].j1 - items[i].j0))) << 32) | uint32_t(i);
+    std::sort(ps.keys.begin(), ps.keys.end());
+    ps.gen.assign(items.begin(), items.end());
+    for (size_t i = 0; i < m; i++) items[i] = ps.gen[uint32_t(ps.keys[i])];
 }
 
 }  // namespace
@@ -126,6 +148,10 @@ struct flint_attn {
     PrefillWorkspace pf;
     int64_t launches = 0;
     std::vector<DecItem> items;
+    PlanScratch plan_scratch;
+    std::vector<int32_t> batch_pos;
+    std::vector<uint32_t> seen;  // per sequence: the number of the last decode batch it appeared in
+    uint32_t batch_no = 0;
     // peer-memory exchange of partial records (KV-range sharding): one cudaMalloc block per rank, opened by the
     // others through CUDA IPC.  Layout: [flags: kMaxPeers words | error word | groups-done counter] in the first 256
     // bytes, then records [2 buffers][ranks][xchg_n][32][130] floats (buffers alternate per step).
@@ -254,15 +280,22 @@ struct flint_attn {
         if (mode == 0 && out_dtype != kDtypeF32 && out_dtype != kDtypeBf16) throw std::runtime_error("bad out dtype");
         if (mode == 0 && kv_ranks > 1 && !L.is_swa)
             throw std::runtime_error("full layers of a KV-sharded handle need decode_partial + combine");
-        std::vector<int32_t> p(n);
+        std::vector<int32_t> &p = batch_pos;
+        p.resize(n);
+        if (seen.size() != size_t(max_seqs)) seen.assign(max_seqs, 0);
+        if (++batch_no == 0) {  // the counter wrapped: forget every stamp
+            std::fill(seen.begin(), seen.end(), 0u);
+            batch_no = 1;
+        }
         for (int i = 0; i < n; i++) {
             p[i] = pos[seqs[i]];
             if (p[i] >= n_ctx) throw std::runtime_error("context full");  // src/engine.mm:904
-            for (int j = 0; j < i; j++)
-                if (seqs[j] == seqs[i]) throw std::runtime_error("a sequence appears twice in one decode batch");
+            if (seen[seqs[i]] == batch_no) throw std::runtime_error("a sequence appears twice in one decode batch");
+            seen[seqs[i]] = batch_no;
         }
         int n_groups = 0, n_records = 0, n_subs = 0;
-        plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records, n_subs);
+        plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records, n_subs,
+                    plan_scratch);
         ensure_scratch(n_records, n_subs, n_groups);
         const bool inline_items = items.size() <= size_t(kMaxParamItems);
         DecParams dp{};
@@ -706,9 +739,10 @@ void *flint_attn_kv_dev(flint_attn *a, int32_t layer, int32_t which) {
 
 int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, int32_t kv_lo, int32_t kv_hi,
                                int32_t target_items, int32_t *out, int32_t cap) {
-    std::vector<DecItem> items;
+    static thread_local std::vector<DecItem> items;
+    static thread_local PlanScratch scratch;
     int n_groups = 0, n_records = 0, n_subs = 0;
-    plan_decode(n, nullptr, pos, is_swa != 0, kv_lo, kv_hi, target_items, items, n_groups, n_records, n_subs);
+    plan_decode(n, nullptr, pos, is_swa != 0, kv_lo, kv_hi, target_items, items, n_groups, n_records, n_subs, scratch);
     if (int(items.size()) > cap) return -1;
     for (size_t i = 0; i < items.size(); i++) {
         const DecItem &it = items[i];
