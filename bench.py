@@ -43,9 +43,10 @@ def decode_bytes(n_seq: int, n_cached: int) -> int:
 
 
 def prefill_flops(n_tok: int, window: int = 513) -> int:
-    """4 * 128 * 32 * sum_p min(p+1, window): QK^T and PV over the causal band only."""
+    """4 * 128 * 32 * sum_p min(p+1, window): QK^T and PV over the causal band only (window = 0: no window)."""
     p = np.arange(n_tok, dtype=np.int64)
-    return int(4 * 128 * 32 * np.minimum(p + 1, window).sum())
+    keys = np.minimum(p + 1, window) if window else p + 1
+    return int(4 * 128 * 32 * keys.sum())
 
 
 class ClockSampler:
@@ -207,12 +208,12 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
-def measure_prefill(torch, fa, fo, local, iters: int, warmup: int):
-    """Prefill workload: one 4000-token prompt on a sliding-window layer (window 512 + sink, causal), bf16 q/k/v rows,
-    positions 0..3999, K/V into the 1024-slot ring.  L2 is flushed between iterations.  Returns a dict."""
+def measure_prefill(torch, fa, fo, local, iters: int, warmup: int, T: int = PREFILL_T, swa: bool = True):
+    """Prefill workload: one T-token prompt (default 4000) on a sliding-window layer (window 512 + sink, causal; K/V
+    into the 1024-slot ring) or, with swa=False, on a full-attention layer (causal over the whole prompt), bf16 q/k/v
+    rows, positions 0..T-1.  L2 is flushed between iterations.  Returns a dict."""
     _, tensor_peak, peak_kind = measured_peaks()
-    T = PREFILL_T
-    h = fa.Attn([True], [True], 1, T + 96, device=local)
+    h = fa.Attn([swa], [True], 1, T + 96, device=local)
     h.set_layer(0, *fo.layer_weights(0, 0))
     gen = torch.Generator(device="cuda").manual_seed(4321)
     qkv = torch.randn(T, QKV_DIM, generator=gen, device="cuda").to(torch.bfloat16)
@@ -239,7 +240,7 @@ def measure_prefill(torch, fa, fo, local, iters: int, warmup: int):
     h.check()
     attn_us = attn_ms / max(n, 1) * 1e3
     step_us = float(np.median([a.elapsed_time(b) for a, b in step_ms])) * 1e3
-    flops = prefill_flops(T)
+    flops = prefill_flops(T, 513 if swa else 0)
     tflops = flops / (attn_us * 1e-6) / 1e12
     # end to end through the host-buffer entry point
     qkv_host, out_host = qkv.cpu().pin_memory(), torch.empty(T, OUT_DIM, dtype=torch.bfloat16).pin_memory()
@@ -251,7 +252,9 @@ def measure_prefill(torch, fa, fo, local, iters: int, warmup: int):
         e2e.append(time.perf_counter() - t0)
     e2e_us = float(np.median(e2e[3:])) * 1e6
     h.close()
-    return {"workload": "prefill: one 4000-token prompt, SWA layer (window 512 + sink, causal), bf16 rows, ring write",
+    kind = "SWA layer (window 512 + sink, causal), bf16 rows, ring write" if swa else \
+        "full-attention layer (causal + sink), bf16 rows, cache write"
+    return {"workload": f"prefill: one {T}-token prompt, {kind}",
             "algorithmic_flops": flops, "attn_kernel_us": attn_us, "tflops": tflops, "peak_tflops": tensor_peak,
             "frac": tflops / tensor_peak, "peak_kind": f"of {peak_kind} (burst)", "step_us": step_us,
             "tok_per_s": T / (step_us * 1e-6), "iters": n, "l2": "flushed between iterations (256 MiB write)",
@@ -387,13 +390,16 @@ def run_prefill_only(args):
     if rank != 0:
         return
     with ClockSampler(local) as clk:
-        pf = measure_prefill(torch, fa, fo, local, iters=args.steps, warmup=args.warmup)
+        pf = measure_prefill(torch, fa, fo, local, iters=args.steps, warmup=args.warmup, T=args.prefill_tokens,
+                             swa=args.prefill_kind == "swa")
+    default_cfg = args.prefill_tokens == PREFILL_T and args.prefill_kind == "swa"
     line = {"metric": "prefill_attn_tflops", "value": pf["tflops"], "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": pf["step_us"] * 1e-3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16 tensor-core products (tcgen05 kind::f16), f32 accumulate/softmax",
             "data": "synthetic", "config": {"workload": pf["workload"], "l2": pf["l2"]},
             "roofline": {"bound": "tensor", "achieved": pf["tflops"], "peak": pf["peak_tflops"], "unit": "TFLOP/s",
-                         "frac": pf["frac"], "traffic": PREFILL_NCU_DRAM_BYTES_PER_LAUNCH, "peak_kind": pf["peak_kind"],
+                         "frac": pf["frac"], "traffic": PREFILL_NCU_DRAM_BYTES_PER_LAUNCH if default_cfg else None,
+                         "peak_kind": pf["peak_kind"],
                          "kernel": "k_prefill_attn",
                          "kernel_us": pf["attn_kernel_us"], "flops_per_launch": pf["algorithmic_flops"]},
             "e2e": {"value": pf["e2e_tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": pf["h2d_bytes_per_step"],
@@ -639,6 +645,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "ragged"])
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="prefill workload: prompt length")
+    ap.add_argument("--prefill-kind", default="swa", choices=["swa", "full"],
+                    help="prefill workload: sliding-window ring layer (the configuration the metric is quoted on) or full attention")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="longctx on several GPUs: partial records through peer memory by the kernels, or by NCCL")
     ap.add_argument("--skip-prefill", action="store_true", help="decode workload only (profiling runs)")

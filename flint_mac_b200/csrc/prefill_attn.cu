@@ -16,6 +16,14 @@
 
 #include <cuda.h>
 
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <queue>
+#include <utility>
+#include <vector>
+
 #include "ptx.cuh"
 #include "tc5.cuh"
 
@@ -49,7 +57,10 @@ constexpr int kPBytes = kBM * kBN * 2;        // 32 KiB per P tile (two 64-key h
 constexpr int kOffStage = kOffKV + kSlots * kTileBytes;  // per Q tile 32 KiB: P tiles, and the output rows at the end of a unit
 static_assert(kPBytes == 2 * kOutBlockBytes, "P and the output staging share one block per Q tile");
 constexpr int kOffBar = kOffStage + kQTiles * 2 * kOutBlockBytes;
-constexpr int kSmemBytes = kOffBar + 256;  // 229632 B: one CTA per SM
+constexpr int kOffSched = kOffBar + 256;   // this CTA's list of work units (the first kSchedLocal of them)
+constexpr int kSchedLocal = 640;
+constexpr int kSmemBytes = kOffSched + kSchedLocal * 4;  // 232192 B: one CTA per SM
+static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 
 #ifdef FLINT_PF_TRACE
 #define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 60) a.trace[(slot)] = clock64(); } while (0)
@@ -59,6 +70,8 @@ constexpr int kSmemBytes = kOffBar + 256;  // 229632 B: one CTA per SM
 
 struct PfArgs {
     long long *trace;  // debug timeline (only with FLINT_PF_TRACE)
+    const int *sched;  // [n_rounds][gridDim.x] unit of CTA b in its round i, -1 = none; nullptr: round-robin
+    int n_rounds, n_units;
     const __half *q_st;  // [32][n_tok][128] normalised, rotated, pre-scaled queries
     void *out;
     const float *sinks;
@@ -225,7 +238,20 @@ __device__ __forceinline__ Unit unit_geom(const PfArgs &a, int u) {
     return g;
 }
 
-// Persistent: one CTA per SM, 320 threads, each CTA walks the units blockIdx.x, blockIdx.x + gridDim.x, ...
+// The i-th unit of this CTA, or -1.  The host balances the units over the CTAs by their tile counts and lays each
+// CTA's list out longest first; the CTA copies its list into shared memory at start (entries past kSchedLocal stay
+// in global memory).  Without a table (at most one unit per CTA, or FLINT_ATTN_PREFILL_SCHEDULE=roundrobin in the
+// environment) CTA b takes units b, b + grid, ...
+__device__ __forceinline__ int unit_at(const PfArgs &a, const int *local, int i) {
+    if (!a.sched) {
+        const int u = int(blockIdx.x) + i * int(gridDim.x);
+        return u < a.n_units ? u : -1;
+    }
+    if (i >= a.n_rounds) return -1;
+    return i < kSchedLocal ? local[i] : __ldg(a.sched + size_t(i) * gridDim.x + blockIdx.x);
+}
+
+// Persistent: one CTA per SM, 384 threads, each CTA walks its list of units.
 // Warps 0-3 own Q tile 0 of the unit (128 rows, one row per thread), warps 4-7 Q tile 1; warp 8 streams Q, K and V
 // tiles with TMA (K and V alternate through a ring of three 32 KiB slots); warp 9 issues every tcgen05.mma.  The two
 // Q tiles share each K/V tile and alternate on the tensor core: while one tile's warps run the softmax of a key tile,
@@ -248,8 +274,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    const int n_units = ((a.n_tok + kCtaPos - 1) / kCtaPos) * kNHeadKv;
     if (tid == 0) PF_TRACE(999);
+    int *sched_local = reinterpret_cast<int *>(gen + kOffSched);
+    if (a.sched)
+        for (int i = tid; i < min(a.n_rounds, kSchedLocal); i += kThreadsAttn)
+            sched_local[i] = a.sched[size_t(i) * gridDim.x + blockIdx.x];
 
     if (tid == 0) {
         for (int i = 0; i < kNumBars; i++) {
@@ -300,8 +329,9 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 tc5::tma_load_3d(dst + kQBytes / 2, &tm_q, full, 64, un.t0 + w * kQPos, un.kvh * kGqa);
                 return true;
             };
-            int i = 0;
-            for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, i++) {
+            for (int i = 0; ok; i++) {
+                const int u = unit_at(a, sched_local, i);
+                if (u < 0) break;
                 const Unit un = unit_geom(a, u);
                 // order of need: Q0, K(0), Q1, V(0), K(1), V(1), ...
                 ok = load_q(un, 0, i) && load_tile(&tm_k, un, 0) && load_q(un, 1, i);
@@ -326,7 +356,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         // its V in ring use 2j + 1.  For each tile and Q tile w: P.V, then Q.K^T of the NEXT tile of the stream (S of w
         // is free again: its P is consumed by the product just issued, in order), possibly of the next unit.
         struct Cursor {
-            int u, i, kt, j;  // unit, index of the unit in this CTA, tile in the unit, tile in the stream
+            int i, kt, j;  // index of the unit in this CTA's list, tile in the unit, tile in the stream
             Unit un;
         };
         // keys of a tile that any query of the unit can see, rounded up to the MMA's N granularity
@@ -335,11 +365,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             if (c.kt + 1 < c.un.n_tiles) {
                 c.kt++;
             } else {
-                c.u += gridDim.x;
-                if (c.u >= n_units) return false;
+                const int u = unit_at(a, sched_local, c.i + 1);
+                if (u < 0) return false;
                 c.i++;
                 c.kt = 0;
-                c.un = unit_geom(a, c.u);
+                c.un = unit_geom(a, u);
             }
             c.j++;
             return true;
@@ -381,8 +411,8 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);
             return true;
         };
-        if (int(blockIdx.x) < n_units) {
-            Cursor cur{int(blockIdx.x), 0, 0, 0, unit_geom(a, blockIdx.x)};
+        if (unit_at(a, sched_local, 0) >= 0) {
+            Cursor cur{0, 0, 0, unit_geom(a, unit_at(a, sched_local, 0))};
             ok = issue_qk(0, cur) && issue_qk(1, cur);
             while (ok) {
                 Cursor nxt = cur;
@@ -414,8 +444,9 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         const uint32_t lane_base = tmem + (uint32_t((warp & 3) * 32) << 16);
         const uint32_t colS = lane_base + kColS + w * kBN, colO = lane_base + kColO + w * kHeadDim;
         int j = 0;  // tiles of the stream seen so far (phase of the S / P / P.V barriers)
-        int i = 0;
-        for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, i++) {
+        for (int i = 0; ok; i++) {
+        const int u = unit_at(a, sched_local, i);
+        if (u < 0) break;
         const Unit un = unit_geom(a, u);
         const int kvh = un.kvh, t0 = un.t0, klo = un.klo, n_keys = un.n_keys, n_tiles = un.n_tiles;
         const int qt_first = un.q_first + w * kQPos;  // first / last position of this Q tile
@@ -670,6 +701,49 @@ cudaError_t make_out_map(CUtensorMap *map, void *base, int n_tok, int out_dtype)
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// Which CTA runs which units.  Units differ in length (the first query blocks of a prompt see fewer keys; on a full
+// layer the band grows with the position), so handing them out round-robin leaves some CTAs with up to a third more
+// tiles than others.  Greedy longest-first assignment to the least loaded CTA by (key tiles + one tile of per-unit
+// overhead); unit indices are already ordered longest first.  The table is kept until the geometry changes.
+cudaError_t build_schedule(PrefillWorkspace &ws, const PfArgs &a, int n_units, int grid, cudaStream_t stream) {
+    const int key[5] = {a.n_tok, a.p0, a.is_swa, a.key_row0, grid};
+    if (ws.sched && memcmp(key, ws.sched_key, sizeof(key)) == 0) return cudaSuccess;
+    const int n_qb = (a.n_tok + kCtaPos - 1) / kCtaPos;
+    std::vector<std::vector<int>> lists(grid);
+    std::priority_queue<std::pair<int, int>, std::vector<std::pair<int, int>>, std::greater<std::pair<int, int>>> heap;
+    for (int b = 0; b < grid; b++) heap.push({0, b});
+    for (int u = 0; u < n_units; u++) {
+        const int t0 = (n_qb - 1 - u / kNHeadKv) * kCtaPos;  // as unit_geom
+        const int q_first = a.p0 + t0, q_last = a.p0 + std::min(t0 + kCtaPos, a.n_tok) - 1;
+        const int klo = a.is_swa ? std::max(q_first - kHist, a.key_row0) : 0;
+        const int tiles = (q_last - klo + 1 + kBN - 1) / kBN;
+        const auto [load, b] = heap.top();
+        heap.pop();
+        lists[b].push_back(u);
+        heap.push({load + tiles + 1, b});
+    }
+    size_t rounds = 0;
+    for (const auto &l : lists) rounds = std::max(rounds, l.size());
+    std::vector<int> table(rounds * grid, -1);
+    for (int b = 0; b < grid; b++)
+        for (size_t i = 0; i < lists[b].size(); i++) table[i * grid + b] = lists[b][i];
+    cudaError_t e;
+    if (table.size() > ws.sched_cap) {
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return e;  // an earlier launch may still read the old one
+        cudaFree(ws.sched);
+        ws.sched = nullptr;
+        ws.sched_cap = 0;
+        if ((e = cudaMalloc(&ws.sched, table.size() * 2 * sizeof(int))) != cudaSuccess) return e;
+        ws.sched_cap = table.size() * 2;
+    }
+    // pageable source: staged by the runtime before the call returns, ordered on the stream behind earlier launches
+    if ((e = cudaMemcpyAsync(ws.sched, table.data(), table.size() * sizeof(int), cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+        return e;
+    memcpy(ws.sched_key, key, sizeof(key));
+    ws.sched_rounds = int(rounds);
+    return cudaSuccess;
+}
+
 }  // namespace
 
 cudaError_t prefill_kernel_setup() {
@@ -688,8 +762,8 @@ cudaError_t prefill_kernel_setup() {
 
 void prefill_workspace_free(PrefillWorkspace &ws) {
     cudaFree(ws.buf);
-    ws.buf = nullptr;
-    ws.cap = 0;
+    cudaFree(ws.sched);
+    ws = PrefillWorkspace{};
 }
 
 cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStream_t stream, int *n_launches) {
@@ -762,6 +836,16 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
     const int n_units = ((T + kCtaPos - 1) / kCtaPos) * kNHeadKv;
     const dim3 grid(n_units < g_sm_count ? n_units : g_sm_count);
+    a.n_units = n_units;
+    static const bool round_robin = [] {
+        const char *v = getenv("FLINT_ATTN_PREFILL_SCHEDULE");
+        return v && strcmp(v, "roundrobin") == 0;
+    }();
+    if (n_units > int(grid.x) && !round_robin) {
+        if ((e = build_schedule(ws, a, n_units, int(grid.x), stream)) != cudaSuccess) return e;
+        a.sched = ws.sched;
+        a.n_rounds = ws.sched_rounds;
+    }
     if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
     k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
     if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);

@@ -22,6 +22,11 @@ struct PrefillParams {
 struct PrefillWorkspace {
     void *buf = nullptr;
     size_t cap = 0;
+    // which CTA runs which work units (see launch_prefill); rebuilt only when the launch geometry changes
+    int *sched = nullptr;
+    size_t sched_cap = 0;
+    int sched_key[5] = {-1, -1, -1, -1, -1};  // n_tok, p0, is_swa, first key row, grid
+    int sched_rounds = 0;
 };
 
 cudaError_t prefill_kernel_setup();

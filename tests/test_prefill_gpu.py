@@ -120,6 +120,28 @@ def test_config3_4000_token_prompt_swa_bf16(fa, fo):
         assert_close(out[some], want2, "config 3, early positions")
 
 
+def test_long_prompt_on_a_full_layer_in_two_chunks(fa, fo):
+    """A 6000-token prompt on a full-attention layer (every key back to position 0), given as a 4000-token chunk and a
+    2000-token chunk that attends over the first chunk's cache; sampled positions against the oracle, cache rows
+    bit for bit through V."""
+    seed, T, cut = 5, 6000, 4000
+    w = fo.layer_weights(seed, 0)
+    qkv, bits = bf16_round_rows(fo.raw_qkv(seed, 0, 0, T))
+    with _open(fa, "full_rope", T + 8) as h:
+        h.set_layer(0, *w)
+        out = np.empty((T, 4096), np.float32)
+        h.prefill(0, 0, cut, bits[:cut], fa.BF16, out[:cut], fa.F32)
+        assert h.advance([0], cut) == 0
+        h.prefill(0, 0, T - cut, np.ascontiguousarray(bits[cut:]), fa.BF16, out[cut:], fa.F32)
+        assert np.isfinite(out).all()
+        some = [0, 1, 127, 128, 2047, 3999, 4000, 4001, 4127, 5000, 5998, 5999]
+        want, kc, vc = oracle_at_positions(qkv, w, False, True, some)
+        assert_close(out[some], want, "full layer, long prompt")
+        k_dev, v_dev = h.read_kv(0, 0, 0, T)
+        for p in (0, 3999, 4000, 5999):
+            assert np.array_equal(v_dev[:, p].reshape(-1), fo.to_f16_bits(vc[p])), p
+
+
 @pytest.mark.parametrize("kind", ["swa_rope", "full_rope"])
 def test_prefill_then_decode_equals_decode_only(fa, fo, kind):
     """The reference's check-prefill idea (src/main.mm:317-346) at the kernel level: prefill the first part, decode the
