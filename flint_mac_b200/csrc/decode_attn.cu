@@ -145,9 +145,12 @@ __device__ __forceinline__ void publish_group(const DecParams &p, int tid) {
     __threadfence_system();  // cumulative over the CTA's stores, which the barrier ordered before it
     if (atomicAdd(p.groups_done, 1) == p.n_groups - 1) {
         *p.groups_done = 0;
+        // ONE system-scope fence orders every record store (this CTA's and, through the counter, the other groups')
+        // before the flag stores; the flag stores themselves are relaxed, so the peers are written back to back
+        // instead of one fence round trip per peer.
         __threadfence_system();
         for (int t = 0; t < p.n_peers; t++)
-            asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(p.peer_flag[t] + p.rank), "r"(p.step) : "memory");
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;\n" ::"l"(p.peer_flag[t] + p.rank), "r"(p.step) : "memory");
     }
 }
 
