@@ -30,10 +30,10 @@ B_PER_GPU, CTX, QKV_DIM, OUT_DIM = 64, 8192, 5120, 4096
 KV_BYTES_PER_KEY = 2048  # K + V, 4 KV heads x 128 dims x fp16, each read once per GQA group
 PREFILL_T = 4000
 # DRAM traffic of one k_decode_attn launch on the default workload, from the committed ncu capture
-# (profiles/k_decode_attn_64x8192.md): 1.074919 GB read + 4.06 MB written.
-DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1074919000 + 4060416
+# (profiles/k_decode_attn_64x8192.md): 1.074846 GB read + 5.34 MB written.
+DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1074846000 + 5344512
 # Same for k_prefill_attn on the 4000-token workload (profiles/k_prefill_attn_4000tok_swa.md).
-PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41029632 + 1384448
+PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41030912 + 1440256
 
 
 def decode_bytes(n_seq: int, n_cached: int) -> int:
