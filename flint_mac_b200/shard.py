@@ -1,6 +1,6 @@
 """Host-side placement for multi-GPU runs: which rank owns which sequence, and which key range.
 
-The reference is single-GPU, single-session; this is the scheduling that SURVEY-level configs add on top:
+The reference is single-GPU, single-session; this is the scheduling that the batched and long-context workloads add:
 independent sequences are spread over ranks by KV bytes (no data-path collective), and one long sequence is cut
 into contiguous key ranges (one exchange step: an all-gather of per-rank partial records).
 """
