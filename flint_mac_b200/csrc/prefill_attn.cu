@@ -476,28 +476,6 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 return 1;
             };
 
-            // Band-edge tiles (the first and the last of a unit) first get their invisible scores overwritten with -inf
-            // in tensor memory by a small loop; after that every tile runs the same straight-line code, which stays
-            // small enough for the instruction cache.
-            if (chunk_kind(0) != 0 || chunk_kind(n_chunks - 1) != 0) {
-#pragma unroll 1
-                for (int ch = 0; ch < n_chunks; ch++) {
-                    const int kind = chunk_kind(ch);
-                    if (kind == 0) continue;
-                    uint32_t t32[32];
-                    if (kind == 1) {
-                        tc5::tmem_ld32(colS + ch * 32, t32);
-                        tc5::tmem_wait_ld();
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c++) {
-                        const int col = ch * 32 + c;
-                        if (kind == 2 || col < c_lo || col > c_hi) t32[c] = 0xff800000u;  // -inf
-                    }
-                    tc5::tmem_st32(colS + ch * 32, t32);
-                }
-                tc5::tmem_wait_st();
-            }
             // the whole row of S into registers: all loads in flight at once, one wait
             uint32_t sr[kBN];
 #pragma unroll
@@ -506,6 +484,19 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             tc5::tmem_wait_ld();
             tc5::fence_before_sync();
             tc5::mbar_arrive(bar(kBarSFree + w));  // S is in registers: the next scores may overwrite it
+            // Band-edge tiles (the first and the last of a unit): invisible scores become -inf, per 32-column chunk and
+            // only in chunks that some row of the Q tile sees partly; interior tiles skip all of it on uniform branches.
+            if (chunk_kind(0) != 0 || chunk_kind(n_chunks - 1) != 0) {
+                const uint32_t span = uint32_t(c_hi - c_lo);
+#pragma unroll
+                for (int ch = 0; ch < kBN / 32; ch++) {
+                    if (ch < n_chunks && chunk_kind(ch) != 0) {
+#pragma unroll
+                        for (int c = 0; c < 32; c++)  // visible iff c_lo <= col <= c_hi
+                            if (uint32_t(ch * 32 + c - c_lo) > span) sr[ch * 32 + c] = 0xff800000u;
+                    }
+                }
+            }
             float mx = -INFINITY;
 #pragma unroll
             for (int ch = 0; ch < kBN / 32; ch++) {
@@ -610,15 +601,18 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                     if (w == 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");  // the four warps of this Q tile only
                     else asm volatile("bar.sync 2, 128;\n" ::: "memory");
                 }
+                // 64 columns of the accumulator row per round: both loads in flight, one wait
+                uint32_t oo[64];
+                tc5::tmem_ld32(colO + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&oo[0]));
+                tc5::tmem_ld32(colO + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&oo[32]));
+                tc5::tmem_wait_ld();
+                if (half == 1) {  // O is in registers: the next unit may overwrite the accumulator
+                    tc5::fence_before_sync();
+                    tc5::mbar_arrive(bar(kBarOFree + w));
+                }
 #pragma unroll
                 for (int q = 0; q < 2; q++) {
-                    uint32_t rr[32];
-                    tc5::tmem_ld32(colO + half * 64 + q * 32, rr);
-                    tc5::tmem_wait_ld();
-                    if (half == 1 && q == 1) {  // O is in registers: the next unit may overwrite the accumulator
-                        tc5::fence_before_sync();
-                        tc5::mbar_arrive(bar(kBarOFree + w));
-                    }
+                    const uint32_t(&rr)[32] = *reinterpret_cast<const uint32_t(*)[32]>(&oo[q * 32]);
                     if (f32) {
                         unsigned char *blk = stg + q * kOutBlockBytes;
 #pragma unroll
