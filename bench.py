@@ -33,7 +33,7 @@ PREFILL_T = 4000
 # (profiles/k_decode_attn_64x8192.md): 1.074846 GB read + 5.34 MB written.
 DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1074846000 + 5344512
 # Same for k_prefill_attn on the 4000-token workload (profiles/k_prefill_attn_4000tok_swa.md).
-PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41030912 + 1440256
+PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41032192 + 1581056
 
 
 def decode_bytes(n_seq: int, n_cached: int) -> int:
