@@ -538,12 +538,15 @@ def run_ragged(args):
     ctx_all = [int(x) for x in rng.integers(1, 32769, n_seq)]
     rolled = rng.random(n_seq) < 0.25
     back_all = [int(b) if r else 0 for b, r in zip(rng.integers(1, 601, n_seq), rolled)]
-    owned = shard.balance_by_kv_bytes(ctx_all, world, n_full_layers=1, n_swa_layers=3)[rank]
+    # --emulate-world N (single GPU only): run rank 0's share of an N-way placement, to look at the per-GPU step of a
+    # multi-GPU run without the other GPUs
+    place_world = args.emulate_world if (world == 1 and args.emulate_world > 1) else world
+    owned = shard.balance_by_kv_bytes(ctx_all, place_world, n_full_layers=1, n_swa_layers=3)[rank]
     ctx = [ctx_all[i] for i in owned]
     back = [min(back_all[i], ctx_all[i]) for i in owned]
     n_loc = len(owned)
     total = args.warmup + args.steps
-    n_ctx = 32768 + total + 8
+    n_ctx = 32768 + total + 100 + 8
     is_swa, has_rope = [True, True, True, False], [True, True, True, False]
     h = fa.Attn(is_swa, has_rope, n_loc, n_ctx, device=local)
     for il in range(4):
@@ -595,7 +598,6 @@ def run_ragged(args):
     for i in range(args.warmup):
         step()
     barrier(world)
-    h.set_timing(True)
     launches0 = h.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
@@ -605,9 +607,17 @@ def run_ragged(args):
         ev1.record()
         barrier(world)
     ms = max_over_ranks(ev0.elapsed_time(ev1), world) / args.steps
+    launches = h.launch_count() - launches0
+    # the kernels alone: a second pass with an event pair around every launch (four short launches per step: the
+    # events would cost the first pass several microseconds per step)
+    k_steps = min(args.steps, 100)
+    h.set_timing(True)
+    for i in range(k_steps):
+        step()
+    torch.cuda.synchronize()
     kernel_ms, n_timed = h.kernel_ms()
     h.set_timing(False)
-    launches = h.launch_count() - launches0
+    kernel_ms = kernel_ms / k_steps * args.steps  # scaled to the step count used below
     my_bytes = sum(step_bytes(args.warmup + i) for i in range(args.steps)) / args.steps
     all_bytes = sum_over_ranks(my_bytes, world)
     max_bytes = max_over_ranks(my_bytes, world)
@@ -621,8 +631,10 @@ def run_ragged(args):
                 "data": "synthetic",
                 "config": {"workload": "ragged serving mix: 256 sequences, context 1..32768 (numpy default_rng(7)), one decode "
                                        "step over 3 SWA ring layers + 1 full layer, 25% rolled back by 1..600 tokens first",
-                           "placement": "greedy LPT by KV bytes", "l2": "inputs larger than L2"},
-                "tok_per_s": n_seq / (ms * 1e-3), "bytes_per_step_all_ranks": all_bytes,
+                           "placement": "greedy LPT by KV bytes", "l2": "inputs larger than L2",
+                           **({"emulated": f"rank 0's share of a {place_world}-way placement on one GPU; value counts this "
+                                           "share only"} if place_world != world else {})},
+                "tok_per_s": (n_loc if place_world != world else n_seq) / (ms * 1e-3), "bytes_per_step_all_ranks": all_bytes,
                 "load_imbalance": max_bytes * world / all_bytes,
                 "roofline": {"bound": "hbm", "achieved": my_bytes / (kernel_step_us * 1e-6) / 1e9, "peak": hbm_peak,
                              "unit": "GB/s", "frac": my_bytes / (kernel_step_us * 1e-6) / 1e9 / hbm_peak, "traffic": None,
@@ -648,6 +660,8 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="prefill workload: prompt length")
     ap.add_argument("--prefill-kind", default="swa", choices=["swa", "full"],
                     help="prefill workload: sliding-window ring layer (the configuration the metric is quoted on) or full attention")
+    ap.add_argument("--emulate-world", type=int, default=1,
+                    help="ragged workload on one GPU: run rank 0's share of an N-way placement")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="longctx on several GPUs: partial records through peer memory by the kernels, or by NCCL")
     ap.add_argument("--skip-prefill", action="store_true", help="decode workload only (profiling runs)")

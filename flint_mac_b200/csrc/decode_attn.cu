@@ -15,6 +15,7 @@
 // the reference's four simdgroups (fused.metal:301-318).  Splits of one (token, KV head) group write fp32 partial
 // records {acc[128], m, l} (fused.metal:324-327); the last CTA of the group to finish (atomic ticket) merges them,
 // so there is no second launch and no spin-wait anywhere.
+#include <cstdlib>
 #include <cstring>
 
 #include "attn_common.h"
@@ -211,6 +212,7 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     const int n_tiles = (j_end - j0 + kTileKeys - 1) / kTileKeys;
     DEC_TRACE(12);
     DEC_TRACE(0);
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // layout of the merge steps at the end: 16 threads per head, 8 dims per thread; the head's sink is fetched now
     const int mh = tid >> 4, md = (tid & 15) * 8;
     const int head = it.kvh * kGqa + mh;
@@ -244,6 +246,17 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     const size_t row0 = size_t(it.tok) * kQkvDim;
     const bool rope = p.has_rope != 0;
     const bool fold_k = it.fold && warp == 0, fold_v = it.fold && warp == 1;
+    const float4 wq = reinterpret_cast<const float4 *>(p.q_norm)[lane];
+    float4 wk = wq;
+    if (fold_k) wk = reinterpret_cast<const float4 *>(p.k_norm)[lane];
+    float freq = 0.f;
+    if (rope && tid < kHeadDim / 2) freq = p.inv_freq[tid];
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled while this one still runs, and
+    // this one may have been scheduled while its predecessor still ran.  Everything above touched only kernel
+    // parameters and the layer's constant tables; nothing produced by an earlier kernel (the q/k/v rows, cache
+    // contents, split-K scratch and counters) is read or written before this wait, which returns once every
+    // earlier kernel of the stream has completed and its writes are visible.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     float4 q[2];
 #pragma unroll
     for (int i = 0; i < 2; i++)
@@ -251,11 +264,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     float4 kv_new = make_float4(0.f, 0.f, 0.f, 0.f);
     if (fold_k) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + size_t(it.kvh) * kHeadDim, lane);
     if (fold_v) kv_new = load_row4(p.qkv, p.qkv_dtype, row0 + kQDim + kKvDim + size_t(it.kvh) * kHeadDim, lane);
-    const float4 wq = reinterpret_cast<const float4 *>(p.q_norm)[lane];
-    float4 wk = wq;
-    if (fold_k) wk = reinterpret_cast<const float4 *>(p.k_norm)[lane];
-    float freq = 0.f;
-    if (rope && tid < kHeadDim / 2) freq = p.inv_freq[tid];
 
 #pragma unroll
     for (int t = 0; t < kStages - 1; t++) {
@@ -550,12 +558,33 @@ constexpr int kCapSmall = 76, kCapMid = 256;
 static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kCapSmall>) <= 4096, "small variant fits 4 KiB of parameters");
 static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kMaxParamItems>) <= 32764, "largest variant fits the limit");
 
+// Launch with programmatic stream serialization: the kernel may be scheduled before its predecessor in the stream
+// has finished (it waits inside, see decode_item), which hides launch latency between the short kernels of a decode
+// step.  FLINT_ATTN_NO_PDL=1 in the environment turns it off.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), int n_items, cudaStream_t stream, const Args &...args) {
+    static const bool off = [] {
+        const char *v = getenv("FLINT_ATTN_NO_PDL");
+        return v && v[0] == '1';
+    }();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(n_items));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = sizeof(DecSmem);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = off ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 template <int kCap>
 cudaError_t launch_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
     static thread_local DecItemsParam<kCap> ip;  // copied into the launch by the runtime before this returns
     memcpy(ip.items, host_items, sizeof(DecItem) * size_t(n_items));
-    k_decode_attn_p<kCap><<<n_items, kThreads, sizeof(DecSmem), stream>>>(p, ip);
-    return cudaGetLastError();
+    return launch_pdl(k_decode_attn_p<kCap>, n_items, stream, p, ip);
 }
 
 // Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.  With a
@@ -615,8 +644,7 @@ cudaError_t decode_kernel_setup() {
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
-    k_decode_attn<<<n_items, kThreads, sizeof(DecSmem), stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(k_decode_attn, n_items, stream, p);
 }
 
 cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
