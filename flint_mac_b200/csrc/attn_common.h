@@ -87,7 +87,8 @@ struct CombineParams {
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream);
 // Same kernel with the work list passed by value in the kernel parameters (n_items <= kMaxParamItems): no upload.
-cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream);
+cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, int sm_count,
+                                 cudaStream_t stream);
 cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream);
 cudaError_t decode_kernel_setup();  // opt-in shared memory size; once per device
 

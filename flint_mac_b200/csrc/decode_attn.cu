@@ -26,7 +26,8 @@ namespace flint {
 namespace {
 
 constexpr int kTileKeys = 64;
-constexpr int kStages = 3;
+constexpr int kStagesWave = 3;   // two CTAs per SM: the usual launch, about one wave of items
+constexpr int kStagesDeep = 6;   // one CTA per SM: launches with no more items than SMs keep twice the bytes in flight
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
 constexpr int kRowBytes = kHeadDim * 2;             // 256
@@ -53,6 +54,7 @@ __device__ __forceinline__ long long global_ns() {
 #define DEC_TRACE(slot) do { } while (0)
 #endif
 
+template <int kStages>
 struct __align__(16) DecSmem {
     unsigned char k[kStages][kTileBytes];
     unsigned char v[kStages][kTileBytes];
@@ -66,7 +68,8 @@ struct __align__(16) DecSmem {
     int is_last;
 };
 // The per-warp output accumulators are merged through the (by then idle) K tiles.
-static_assert(sizeof(float) * kWarps * kGqa * kHeadDim <= kStages * kTileBytes, "merge buffer aliases the K tiles");
+static_assert(sizeof(float) * kWarps * kGqa * kHeadDim <= kStagesWave * kTileBytes, "merge buffer aliases the K tiles");
+static_assert(sizeof(DecSmem<kStagesDeep>) <= 227 * 1024, "one CTA per SM");
 
 __device__ __forceinline__ float4 load_row4(const void *base, int dtype, size_t elem0, int lane) {
     if (dtype == kDtypeF32) return reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem0)[lane];
@@ -201,9 +204,10 @@ __device__ __forceinline__ Merged merge_records(const float *rec, int n, int d0,
     return r;
 }
 
+template <int kStages>
 __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &it) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    DecSmem &sm = *reinterpret_cast<DecSmem *>(smem_raw);
+    DecSmem<kStages> &sm = *reinterpret_cast<DecSmem<kStages> *>(smem_raw);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
@@ -544,14 +548,14 @@ struct DecItemsParam {
 
 __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
     const DecItem it = p.items[blockIdx.x];
-    decode_item(p, it);
+    decode_item<kStagesWave>(p, it);
 }
 
-template <int kCap>
-__global__ void __launch_bounds__(kThreads, 2) k_decode_attn_p(const __grid_constant__ DecParams p,
-                                                               const __grid_constant__ DecItemsParam<kCap> ip) {
+template <int kCap, int kStages>
+__global__ void __launch_bounds__(kThreads, kStages == kStagesWave ? 2 : 1)
+    k_decode_attn_p(const __grid_constant__ DecParams p, const __grid_constant__ DecItemsParam<kCap> ip) {
     const DecItem it = ip.items[blockIdx.x];
-    decode_item(p, it);
+    decode_item<kStages>(p, it);
 }
 
 constexpr int kCapSmall = 76, kCapMid = 256;
@@ -562,7 +566,8 @@ static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kMaxParamItems>) <= 32764
 // has finished (it waits inside, see decode_item), which hides launch latency between the short kernels of a decode
 // step.  FLINT_ATTN_NO_PDL=1 in the environment turns it off.
 template <typename... KArgs, typename... Args>
-cudaError_t launch_pdl(void (*kernel)(KArgs...), int n_items, cudaStream_t stream, const Args &...args) {
+cudaError_t launch_pdl(void (*kernel)(KArgs...), int n_items, size_t smem_bytes, cudaStream_t stream,
+                       const Args &...args) {
     static const bool off = [] {
         const char *v = getenv("FLINT_ATTN_NO_PDL");
         return v && v[0] == '1';
@@ -570,7 +575,7 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), int n_items, cudaStream_t strea
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(unsigned(n_items));
     cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = sizeof(DecSmem);
+    cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr{};
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -580,11 +585,16 @@ cudaError_t launch_pdl(void (*kernel)(KArgs...), int n_items, cudaStream_t strea
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-template <int kCap>
+template <int kCap, int kStages>
 cudaError_t launch_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
     static thread_local DecItemsParam<kCap> ip;  // copied into the launch by the runtime before this returns
     memcpy(ip.items, host_items, sizeof(DecItem) * size_t(n_items));
-    return launch_pdl(k_decode_attn_p<kCap>, n_items, stream, p, ip);
+    return launch_pdl(k_decode_attn_p<kCap, kStages>, n_items, sizeof(DecSmem<kStages>), stream, p, ip);
+}
+
+template <typename K>
+cudaError_t allow_smem(K kernel, size_t bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes));
 }
 
 // Merge of per-device partial records (KV-range sharding): one CTA per (token, head), thread = dim.  With a
@@ -632,27 +642,34 @@ __global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams 
 }  // namespace
 
 cudaError_t decode_kernel_setup() {
-    const int bytes = int(sizeof(DecSmem));
-    cudaError_t e = cudaFuncSetAttribute(k_decode_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k_decode_attn_p<kCapSmall>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k_decode_attn_p<kCapMid>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(k_decode_attn_p<kMaxParamItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    constexpr size_t wave = sizeof(DecSmem<kStagesWave>), deep = sizeof(DecSmem<kStagesDeep>);
+    cudaError_t e = allow_smem(k_decode_attn, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesWave>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesWave>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kMaxParamItems, kStagesWave>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesDeep>, deep);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesDeep>, deep);
+    return e;
 }
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
-    return launch_pdl(k_decode_attn, n_items, stream, p);
+    return launch_pdl(k_decode_attn, n_items, sizeof(DecSmem<kStagesWave>), stream, p);
 }
 
-cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
+cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, int sm_count,
+                                 cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
     if (n_items > kMaxParamItems) return cudaErrorInvalidValue;
-    if (n_items <= kCapSmall) return launch_inline<kCapSmall>(p, host_items, n_items, stream);
-    if (n_items <= kCapMid) return launch_inline<kCapMid>(p, host_items, n_items, stream);
-    return launch_inline<kMaxParamItems>(p, host_items, n_items, stream);
+    // No more items than SMs: every CTA has an SM to itself, so it takes the deep pipeline (twice the bytes in flight
+    // per SM; a short launch is bound by latency, not by bandwidth).
+    if (n_items <= sm_count && n_items <= kCapMid) {
+        if (n_items <= kCapSmall) return launch_inline<kCapSmall, kStagesDeep>(p, host_items, n_items, stream);
+        return launch_inline<kCapMid, kStagesDeep>(p, host_items, n_items, stream);
+    }
+    if (n_items <= kCapSmall) return launch_inline<kCapSmall, kStagesWave>(p, host_items, n_items, stream);
+    if (n_items <= kCapMid) return launch_inline<kCapMid, kStagesWave>(p, host_items, n_items, stream);
+    return launch_inline<kMaxParamItems, kStagesWave>(p, host_items, n_items, stream);
 }
 
 cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream) {

@@ -333,7 +333,7 @@ struct flint_attn {
             dp.n_groups = n_groups;
         }
         time_mark(st);
-        if (inline_items) CK(launch_decode_inline(dp, items.data(), int(items.size()), st));
+        if (inline_items) CK(launch_decode_inline(dp, items.data(), int(items.size()), sm_count, st));
         else CK(launch_decode(dp, int(items.size()), st));
         time_mark(st);
         launches++;
