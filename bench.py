@@ -368,7 +368,9 @@ def run_decode(args):
                          "kernel": "k_decode_attn", "kernel_us": kernel_ms_avg * 1e3, "bytes_per_launch": step_bytes},
             "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": B_PER_GPU * QKV_DIM * 2, "d2h_bytes_per_step": B_PER_GPU * OUT_DIM * 2,
-                    "tok_per_s": B_PER_GPU * world / (e2e_ms * 1e-3), "checksum": checksum},
+                    "tok_per_s": B_PER_GPU * world / (e2e_ms * 1e-3), "checksum": checksum,
+                    "path": "flint_attn_decode: rows copied in from page-locked host memory, output rows written by the "
+                            "kernel into page-locked host memory, stream synchronised, every step"},
             "gpu_launches": launches,
             "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                              "sample": "4 of 64 sequences x 2 repeats of the same step, OpenMP over heads",

@@ -612,9 +612,18 @@ int32_t flint_attn_decode(flint_attn *a, int32_t layer, int32_t n, const int32_t
     const size_t out_bytes = size_t(n) * kQDim * elem_size(out_dtype);
     a->ensure_io(in_pad + out_bytes);
     char *d_in = static_cast<char *>(a->io_dev), *d_out = d_in + in_pad;
+    // Output rows in page-locked host memory are written by the kernel itself (posted writes over PCIe that overlap
+    // the kernel's tail) instead of being staged on the device and copied back.
+    void *out_mapped = nullptr;
+    cudaPointerAttributes attr{};
+    if (cudaPointerGetAttributes(&attr, out) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer &&
+        (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15) == 0)
+        out_mapped = attr.devicePointer;
+    else
+        cudaGetLastError();  // pageable memory makes the query fail on some drivers: not an error here
     CK(cudaMemcpyAsync(d_in, qkv, in_bytes, cudaMemcpyHostToDevice, a->stream));
-    a->decode_dev(layer, n, seqs, d_in, qkv_dtype, d_out, out_dtype, nullptr, 0, a->stream);
-    CK(cudaMemcpyAsync(out, d_out, out_bytes, cudaMemcpyDeviceToHost, a->stream));
+    a->decode_dev(layer, n, seqs, d_in, qkv_dtype, out_mapped ? out_mapped : d_out, out_dtype, nullptr, 0, a->stream);
+    if (!out_mapped) CK(cudaMemcpyAsync(out, d_out, out_bytes, cudaMemcpyDeviceToHost, a->stream));
     CK(cudaStreamSynchronize(a->stream));  // synchronous like the reference (src/engine.mm:930)
     return 0;
     API_CATCH(-1)

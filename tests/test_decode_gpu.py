@@ -311,3 +311,32 @@ def test_exchange_wait_is_bounded(fa, fo):
     finally:
         for h in handles:
             h.close()
+
+
+def test_host_entry_with_page_locked_output_rows(fa, fo):
+    """flint_attn_decode writes its output rows straight into page-locked host memory (no staging copy); pageable
+    rows go through the device staging buffer.  Both give the same bits."""
+    import torch
+
+    seed, B, S = 31, 5, 700
+    w = fo.layer_weights(seed, 0)
+    rows, bits = bf16_round_rows(np.stack([fo.raw_qkv(seed, 0, S, 1, seq=s)[0] for s in range(B)]))
+    outs = []
+    for pinned in (False, True):
+        with _open(fa, ["full_rope"], B, 1024) as h:
+            h.set_layer(0, *w)
+            for s in range(B):
+                k, v = synth_cache_f16(seed, 0, s, S)
+                h.write_kv(0, s, 0, to_slot_layout(k, 1024, False), to_slot_layout(v, 1024, False))
+                h.set_pos(s, S)
+            if pinned:
+                q_host = torch.from_numpy(bits.view(np.int16)).pin_memory()
+                o_host = torch.zeros(B, 4096, dtype=torch.float32).pin_memory()
+                h.decode(0, list(range(B)), q_host, fa.BF16, o_host, fa.F32)
+                outs.append(o_host.numpy().copy())
+            else:
+                o = np.zeros((B, 4096), np.float32)
+                h.decode(0, list(range(B)), bits, fa.BF16, o, fa.F32)
+                outs.append(o)
+    assert np.array_equal(outs[0], outs[1])
+    assert np.abs(outs[0]).max() > 0
