@@ -350,6 +350,8 @@ def run_decode(args):
         t_cpu0 = time.perf_counter()
         sec_per_seq = cpu_decode_sample(0, 1 if args.skip_cpu else 4, CTX, cores, reps=1 if args.skip_cpu else 2)
         cpu_gbs = decode_bytes(1, CTX) / sec_per_seq / 1e9
+        # the reference runs its CPU attention on one thread (threads only in matvec, src/ref/ref_model.cpp:85-92)
+        sec_1t = None if args.skip_cpu else cpu_decode_sample(1, 1, CTX, 1, reps=1)
         line = {
             "metric": "decode_attn_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -374,7 +376,10 @@ def run_decode(args):
             "gpu_launches": launches,
             "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cores, "kind": "port",
                              "sample": "4 of 64 sequences x 2 repeats of the same step, OpenMP over heads",
-                             "tok_per_s": 1.0 / sec_per_seq, "wall_s": time.perf_counter() - t_cpu0},
+                             "tok_per_s": 1.0 / sec_per_seq, "wall_s": time.perf_counter() - t_cpu0,
+                             "single_thread": None if sec_1t is None else
+                             {"value": decode_bytes(1, CTX) / sec_1t / 1e9, "unit": "GB/s", "cores": 1,
+                              "sample": "1 of 64 sequences, one thread (how the reference runs attention)"}},
             "clocks": clk.summary(),
             "prefill": prefill,
         }
