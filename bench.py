@@ -42,9 +42,10 @@ def decode_bytes(n_seq: int, n_cached: int) -> int:
     return n_seq * (KV_BYTES_PER_KEY * n_cached + QKV_DIM * 2 + 2 * 512 * 2 + OUT_DIM * 2)
 
 
-def prefill_flops(n_tok: int, window: int = 513) -> int:
-    """4 * 128 * 32 * sum_p min(p+1, window): QK^T and PV over the causal band only (window = 0: no window)."""
-    p = np.arange(n_tok, dtype=np.int64)
+def prefill_flops(n_tok: int, window: int = 513, p0: int = 0) -> int:
+    """4 * 128 * 32 * sum_p min(p+1, window): QK^T and PV over the causal band only (window = 0: no window), for the
+    positions p0 .. p0+n_tok-1."""
+    p = np.arange(p0, p0 + n_tok, dtype=np.int64)
     keys = np.minimum(p + 1, window) if window else p + 1
     return int(4 * 128 * 32 * keys.sum())
 
@@ -208,14 +209,18 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
-def measure_prefill(torch, fa, fo, local, iters: int, warmup: int, T: int = PREFILL_T, swa: bool = True):
+def measure_prefill(torch, fa, fo, local, iters: int, warmup: int, T: int = PREFILL_T, swa: bool = True,
+                    history: int = 0):
     """Prefill workload: one T-token prompt (default 4000) on a sliding-window layer (window 512 + sink, causal; K/V
     into the 1024-slot ring) or, with swa=False, on a full-attention layer (causal over the whole prompt), bf16 q/k/v
     rows, positions 0..T-1.  L2 is flushed between iterations.  Returns a dict."""
     _, tensor_peak, peak_kind = measured_peaks()
-    h = fa.Attn([swa], [True], 1, T + 96, device=local)
+    h = fa.Attn([swa], [True], 1, history + T + 96, device=local)
     h.set_layer(0, *fo.layer_weights(0, 0))
     gen = torch.Generator(device="cuda").manual_seed(4321)
+    if history:  # a chunk of a longer prompt: the cache already holds `history` tokens
+        for which in (0, 1):
+            as_tensor(torch, h.kv_dev(0, which), 4 * h.n_slots(0) * 128, torch.float16).normal_(generator=gen)
     qkv = torch.randn(T, QKV_DIM, generator=gen, device="cuda").to(torch.bfloat16)
     out = torch.empty(T, OUT_DIM, device="cuda", dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -223,12 +228,13 @@ def measure_prefill(torch, fa, fo, local, iters: int, warmup: int, T: int = PREF
     step_ms = []
     h.set_timing(True)
     for i in range(warmup + iters):
-        h.set_pos(0, 0)
+        h.set_pos(0, history)
         flush.fill_(i & 0xFF)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if i == warmup:
             torch.cuda.synchronize()
             h.kernel_ms()  # drop the warm-up records
+            launches0 = h.launch_count()
         e0.record()
         h.prefill_dev(0, 0, T, qkv, fa.BF16, out, fa.BF16, stream)
         e1.record()
@@ -236,17 +242,18 @@ def measure_prefill(torch, fa, fo, local, iters: int, warmup: int, T: int = PREF
             step_ms.append((e0, e1))
     torch.cuda.synchronize()
     attn_ms, n = h.kernel_ms()
+    launches_per_step = (h.launch_count() - launches0) // max(iters, 1)
     h.set_timing(False)
     h.check()
     attn_us = attn_ms / max(n, 1) * 1e3
     step_us = float(np.median([a.elapsed_time(b) for a, b in step_ms])) * 1e3
-    flops = prefill_flops(T, 513 if swa else 0)
+    flops = prefill_flops(T, 513 if swa else 0, history)
     tflops = flops / (attn_us * 1e-6) / 1e12
     # end to end through the host-buffer entry point
     qkv_host, out_host = qkv.cpu().pin_memory(), torch.empty(T, OUT_DIM, dtype=torch.bfloat16).pin_memory()
     e2e = []
     for i in range(3 + min(iters, 10)):
-        h.set_pos(0, 0)
+        h.set_pos(0, history)
         t0 = time.perf_counter()
         h.prefill(0, 0, T, qkv_host, fa.BF16, out_host, fa.BF16)
         e2e.append(time.perf_counter() - t0)
@@ -254,13 +261,14 @@ def measure_prefill(torch, fa, fo, local, iters: int, warmup: int, T: int = PREF
     h.close()
     kind = "SWA layer (window 512 + sink, causal), bf16 rows, ring write" if swa else \
         "full-attention layer (causal + sink), bf16 rows, cache write"
-    return {"workload": f"prefill: one {T}-token prompt, {kind}",
+    what = f"one {T}-token prompt" if not history else f"a {T}-token chunk after {history} cached tokens"
+    return {"workload": f"prefill: {what}, {kind}",
             "algorithmic_flops": flops, "attn_kernel_us": attn_us, "tflops": tflops, "peak_tflops": tensor_peak,
             "frac": tflops / tensor_peak, "peak_kind": f"of {peak_kind} (burst)", "step_us": step_us,
             "tok_per_s": T / (step_us * 1e-6), "iters": n, "l2": "flushed between iterations (256 MiB write)",
             "e2e_us": e2e_us, "e2e_tok_per_s": T / (e2e_us * 1e-6), "e2e_tflops": flops / (e2e_us * 1e-6) / 1e12,
             "h2d_bytes_per_step": T * QKV_DIM * 2, "d2h_bytes_per_step": T * OUT_DIM * 2,
-            "gpu_launches_per_step": 2, "checksum": float(out_host.float().abs().mean())}
+            "gpu_launches_per_step": launches_per_step, "checksum": float(out_host.float().abs().mean())}
 
 
 def run_decode(args):
@@ -398,8 +406,8 @@ def run_prefill_only(args):
         return
     with ClockSampler(local) as clk:
         pf = measure_prefill(torch, fa, fo, local, iters=args.steps, warmup=args.warmup, T=args.prefill_tokens,
-                             swa=args.prefill_kind == "swa")
-    default_cfg = args.prefill_tokens == PREFILL_T and args.prefill_kind == "swa"
+                             swa=args.prefill_kind == "swa", history=args.prefill_history)
+    default_cfg = args.prefill_tokens == PREFILL_T and args.prefill_kind == "swa" and not args.prefill_history
     line = {"metric": "prefill_attn_tflops", "value": pf["tflops"], "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": pf["step_us"] * 1e-3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16 tensor-core products (tcgen05 kind::f16), f32 accumulate/softmax",
@@ -411,7 +419,7 @@ def run_prefill_only(args):
                          "kernel_us": pf["attn_kernel_us"], "flops_per_launch": pf["algorithmic_flops"]},
             "e2e": {"value": pf["e2e_tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": pf["h2d_bytes_per_step"],
                     "d2h_bytes_per_step": pf["d2h_bytes_per_step"], "us_per_step": pf["e2e_us"]},
-            "gpu_launches": 2 * args.steps, "tok_per_s": pf["tok_per_s"], "clocks": clk.summary()}
+            "gpu_launches": pf["gpu_launches_per_step"] * args.steps, "tok_per_s": pf["tok_per_s"], "clocks": clk.summary()}
     print(json.dumps(line), flush=True)
 
 
@@ -665,6 +673,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "ragged"])
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="prefill workload: prompt length")
+    ap.add_argument("--prefill-history", type=int, default=0,
+                    help="prefill workload: tokens already cached before the timed chunk (chunked prefill)")
     ap.add_argument("--prefill-kind", default="swa", choices=["swa", "full"],
                     help="prefill workload: sliding-window ring layer (the configuration the metric is quoted on) or full attention")
     ap.add_argument("--emulate-world", type=int, default=1,

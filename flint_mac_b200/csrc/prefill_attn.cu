@@ -79,6 +79,10 @@ struct PfArgs {
     int out_dtype;
     int p0, n_tok, is_swa;
     int key_row0;  // key position held by row 0 of the K/V tensor maps
+    // Key-range split (full layers, chunks with fewer units than SMs): every unit is cut into n_ksplit ranges of key
+    // tiles; each range writes an un-normalised fp32 partial (rows s * t_pad + t of `out`) and its (m, l) per row.
+    int n_ksplit, t_pad;
+    float2 *part_ml;  // [n_ksplit * t_pad][32] (m in base-2 units, l)
 };
 
 // ------------------------------------------------------------------------------------------------- prologue
@@ -219,23 +223,40 @@ enum {
     kNumBars = kBarSFree + 2
 };
 
-// A work unit: 32 consecutive query positions (two Q tiles of 16 positions x 8 heads) of one KV head.
+// A work unit: 32 consecutive query positions (two Q tiles of 16 positions x 8 heads) of one KV head, and, when the
+// key range is split, one range of its key tiles.
 struct Unit {
-    int t0, kvh, q_first, q_last, klo, n_keys, n_tiles;
+    int t0, kvh, q_first, q_last, klo, n_keys, n_tiles, split;
 };
 // Units are handed out longest first: late query blocks (full 544-key bands) before the first 16 blocks of the
 // prompt, whose bands are shorter, so that the CTAs that get one unit more than the others get short ones.
-__device__ __forceinline__ Unit unit_geom(const PfArgs &a, int u) {
+// (Host and device: the host's schedule uses the same tile counts.)
+__host__ __device__ inline Unit unit_geom_of(int u, int n_tok, int p0, int is_swa, int key_row0, int n_ksplit) {
     Unit g;
-    const int n_qb = (a.n_tok + kCtaPos - 1) / kCtaPos;
-    g.t0 = (n_qb - 1 - u / kNHeadKv) * kCtaPos;
-    g.kvh = u % kNHeadKv;
-    g.q_first = a.p0 + g.t0;
-    g.q_last = a.p0 + min(g.t0 + kCtaPos, a.n_tok) - 1;
-    g.klo = a.is_swa ? max(g.q_first - kHist, a.key_row0) : 0;
+    const int uq = u / n_ksplit;
+    g.split = u % n_ksplit;
+    const int n_qb = (n_tok + kCtaPos - 1) / kCtaPos;
+    g.t0 = (n_qb - 1 - uq / kNHeadKv) * kCtaPos;
+    g.kvh = uq % kNHeadKv;
+    g.q_first = p0 + g.t0;
+    const int t_end = g.t0 + kCtaPos < n_tok ? g.t0 + kCtaPos : n_tok;
+    g.q_last = p0 + t_end - 1;
+    const int lo_swa = g.q_first - kHist > key_row0 ? g.q_first - kHist : key_row0;
+    g.klo = is_swa ? lo_swa : 0;
     g.n_keys = g.q_last - g.klo + 1;
     g.n_tiles = (g.n_keys + kBN - 1) / kBN;
+    if (n_ksplit > 1) {  // the host guarantees at least 4 tiles per range; the last range takes the remainder
+        const int per = g.n_tiles / n_ksplit;
+        const int kt_a = g.split * per, kt_b = g.split == n_ksplit - 1 ? g.n_tiles : kt_a + per;
+        const int left = g.n_keys - kt_a * kBN;
+        g.klo += kt_a * kBN;
+        g.n_keys = left < (kt_b - kt_a) * kBN ? left : (kt_b - kt_a) * kBN;
+        g.n_tiles = kt_b - kt_a;
+    }
     return g;
+}
+__device__ __forceinline__ Unit unit_geom(const PfArgs &a, int u) {
+    return unit_geom_of(u, a.n_tok, a.p0, a.is_swa, a.key_row0, a.n_ksplit);
 }
 
 // The i-th unit of this CTA, or -1.  The host balances the units over the CTAs by their tile counts and lays each
@@ -454,7 +475,10 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         const int qpos = qt_first + qi;
         const float sink2 = a.sinks[kvh * kGqa + hl] * kLog2e;
 
-        float m = sink2, l = 1.0f;  // prefill.metal:162
+        // prefill.metal:162: the sink enters through m0 = sink, l0 = 1 -- once per row, so with a split key range
+        // only the first range carries it (the others start empty; their first tile is fully visible, so m gets finite)
+        const bool has_sink = un.split == 0;
+        float m = has_sink ? sink2 : -INFINITY, l = has_sink ? 1.0f : 0.0f;
         for (int kt = 0; kt < n_tiles && ok; kt++) {
             if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 0);
             ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + w), j & 1));  // warp-uniform for tcgen05.ld
@@ -516,7 +540,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             float corr = 1.0f;
             if (kt == 0) {
                 m = fmaxf(m, mx);
-                l = fast_exp2(sink2 - m);  // the sink's share of the denominator under the new maximum
+                l = has_sink ? fast_exp2(sink2 - m) : 0.0f;  // the sink's share of the denominator under the new maximum
             } else if (mx > m + 8.0f) {
                 corr = fast_exp2(m - mx);
                 m = mx;
@@ -588,8 +612,12 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             // the blocks to TMA, which writes full lines and clips rows past the prompt.  bf16 rows fit the two staging
             // blocks at once; fp32 rows go out in two rounds.  The TMA store of a unit drains while the next unit runs.
             tc5::fence_after_sync();
-            const float inv_l = 1.0f / l;
+            const bool partial = a.n_ksplit > 1;
+            const float inv_l = partial ? 1.0f : 1.0f / l;
             const bool f32 = a.out_dtype == kDtypeF32;
+            const int row0 = un.t0 + w * kQPos + un.split * a.t_pad;  // row of the output tensor this Q tile starts at
+            if (partial && un.t0 + w * kQPos + qi < a.n_tok)
+                a.part_ml[size_t(row0 + qi) * kNHead + kvh * kGqa + hl] = make_float2(m, l);
             const uint32_t stage_off = kOffStage + w * 2 * kOutBlockBytes;
             unsigned char *stg = gen + stage_off + r * 128;
             const int sw = r & 7;
@@ -642,7 +670,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                     if (r == 0 && tile_valid) {
                         for (int b = 0; b < 2; b++)
                             tc5::tma_store_3d(&tm_o, base + stage_off + b * kOutBlockBytes, f32 ? half * 64 + b * 32 : b * 64,
-                                              t0 + w * kQPos, kvh * kGqa);
+                                              row0, kvh * kGqa);
                         tc5::tma_store_commit();
                     }
                 }
@@ -656,6 +684,37 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
     tc5::fence_before_sync();
     __syncthreads();
     if (warp == 0) tc5::tmem_dealloc(tmem, kTmemCols);
+}
+
+// Merge of the key-range partials of one chunk: out[t][head][:] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+// (the log-sum-exp merge of src/metal/fused.metal:332-350 applied to prefill rows; the sink is inside range 0's l).
+// One CTA per (token, 4 heads), thread = (head, 4 dims).
+__global__ void __launch_bounds__(128) k_prefill_merge(const float *part_o, const float2 *part_ml, void *out, int out_dtype,
+                                                       int n_tok, int t_pad, int n_ksplit) {
+    const int t = blockIdx.x / (kNHead / 4);
+    const int head = (blockIdx.x % (kNHead / 4)) * 4 + (threadIdx.x >> 5);
+    const int d = (threadIdx.x & 31) * 4;
+    float M = -INFINITY;
+    for (int s = 0; s < n_ksplit; s++) M = fmaxf(M, part_ml[(size_t(s) * t_pad + t) * kNHead + head].x);
+    float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_ksplit; s++) {
+        const float2 ml = part_ml[(size_t(s) * t_pad + t) * kNHead + head];
+        const float c = ml.y == 0.f ? 0.f : exp2f(ml.x - M);
+        const float4 o = *reinterpret_cast<const float4 *>(part_o + (size_t(s) * t_pad + t) * kQDim + head * kHeadDim + d);
+        L += ml.y * c;
+        acc[0] += o.x * c; acc[1] += o.y * c; acc[2] += o.z * c; acc[3] += o.w * c;
+    }
+    const float inv = 1.0f / L;
+    const size_t idx = size_t(t) * kQDim + head * kHeadDim + d;
+    if (out_dtype == kDtypeF32) {
+        *reinterpret_cast<float4 *>(static_cast<float *>(out) + idx) =
+            make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+        *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(out) + idx) =
+            make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+    }
 }
 
 // ------------------------------------------------------------------------------------------------- host
@@ -700,17 +759,13 @@ cudaError_t make_out_map(CUtensorMap *map, void *base, int n_tok, int out_dtype)
 // tiles than others.  Greedy longest-first assignment to the least loaded CTA by (key tiles + one tile of per-unit
 // overhead); unit indices are already ordered longest first.  The table is kept until the geometry changes.
 cudaError_t build_schedule(PrefillWorkspace &ws, const PfArgs &a, int n_units, int grid, cudaStream_t stream) {
-    const int key[5] = {a.n_tok, a.p0, a.is_swa, a.key_row0, grid};
+    const int key[5] = {a.n_tok, a.p0, a.is_swa * 256 + a.n_ksplit, a.key_row0, grid};
     if (ws.sched && memcmp(key, ws.sched_key, sizeof(key)) == 0) return cudaSuccess;
-    const int n_qb = (a.n_tok + kCtaPos - 1) / kCtaPos;
     std::vector<std::vector<int>> lists(grid);
     std::priority_queue<std::pair<int, int>, std::vector<std::pair<int, int>>, std::greater<std::pair<int, int>>> heap;
     for (int b = 0; b < grid; b++) heap.push({0, b});
     for (int u = 0; u < n_units; u++) {
-        const int t0 = (n_qb - 1 - u / kNHeadKv) * kCtaPos;  // as unit_geom
-        const int q_first = a.p0 + t0, q_last = a.p0 + std::min(t0 + kCtaPos, a.n_tok) - 1;
-        const int klo = a.is_swa ? std::max(q_first - kHist, a.key_row0) : 0;
-        const int tiles = (q_last - klo + 1 + kBN - 1) / kBN;
+        const int tiles = unit_geom_of(u, a.n_tok, a.p0, a.is_swa, a.key_row0, a.n_ksplit).n_tiles;
         const auto [load, b] = heap.top();
         heap.pop();
         lists[b].push_back(u);
@@ -767,7 +822,19 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
     const size_t q_bytes = up(size_t(kNHead) * T * kHeadDim * 2);
     const size_t kv_bytes = p.is_swa ? up(size_t(kNHeadKv) * (n_hist + T) * kHeadDim * 2) : 0;
-    const size_t need = q_bytes + 2 * kv_bytes + 1024;
+    // Key-range split: a chunk on a full layer with fewer units than SMs and a long history leaves most of the GPU
+    // idle (512 tokens = 64 units) while every unit walks hundreds of key tiles.  Each unit is then cut into ranges
+    // of at least 4 key tiles, as many as fit the SMs, and a small kernel merges the partials.
+    const int n_units_q = ((T + kCtaPos - 1) / kCtaPos) * kNHeadKv;
+    int n_ksplit = 1;
+    if (!p.is_swa && n_units_q * 2 <= g_sm_count) {
+        const int min_tiles = (p.p0 + (T < kCtaPos ? T : kCtaPos) + kBN - 1) / kBN;  // the first query block's tiles
+        n_ksplit = std::max(1, std::min(g_sm_count / n_units_q, min_tiles / 4));
+    }
+    const int t_pad = (T + kCtaPos - 1) / kCtaPos * kCtaPos;
+    const size_t part_o_bytes = n_ksplit > 1 ? up(size_t(n_ksplit) * t_pad * kQDim * sizeof(float)) : 0;
+    const size_t part_ml_bytes = n_ksplit > 1 ? up(size_t(n_ksplit) * t_pad * kNHead * sizeof(float2)) : 0;
+    const size_t need = q_bytes + 2 * kv_bytes + part_o_bytes + part_ml_bytes + 1024;
     if (need > ws.cap) {
         cudaError_t e = cudaDeviceSynchronize();  // an earlier launch may still be reading the old staging
         if (e != cudaSuccess) return e;
@@ -785,6 +852,8 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     __half *q_st = reinterpret_cast<__half *>(wbase + 1024);
     __half *k_st = p.is_swa ? reinterpret_cast<__half *>(wbase + 1024 + q_bytes) : nullptr;
     __half *v_st = p.is_swa ? reinterpret_cast<__half *>(wbase + 1024 + q_bytes + kv_bytes) : nullptr;
+    float *part_o = reinterpret_cast<float *>(wbase + 1024 + q_bytes + 2 * kv_bytes);
+    float2 *part_ml = reinterpret_cast<float2 *>(wbase + 1024 + q_bytes + 2 * kv_bytes + part_o_bytes);
 
     PrologueArgs pa{};
     pa.qkv = p.qkv; pa.q_norm = p.q_norm; pa.k_norm = p.k_norm; pa.inv_freq = p.inv_freq;
@@ -805,7 +874,9 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     (*n_launches)++;
 
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
-    if ((e = make_out_map(&tm_o, p.out, T, p.out_dtype)) != cudaSuccess) return e;
+    if (n_ksplit > 1) e = make_out_map(&tm_o, part_o, n_ksplit * t_pad, kDtypeF32);  // partials: fp32, un-normalised
+    else e = make_out_map(&tm_o, p.out, T, p.out_dtype);
+    if (e != cudaSuccess) return e;
     if ((e = make_map(&tm_q, q_st, T, kNHead, kQPos, kGqa)) != cudaSuccess) return e;
     const void *kb = p.is_swa ? static_cast<const void *>(k_st) : static_cast<const void *>(p.k_cache);
     const void *vb = p.is_swa ? static_cast<const void *>(v_st) : static_cast<const void *>(p.v_cache);
@@ -825,10 +896,13 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     }
 #endif
     a.q_st = q_st;
-    a.out = p.out; a.sinks = p.sinks; a.error_flag = err_flag; a.out_dtype = p.out_dtype;
+    a.out = n_ksplit > 1 ? static_cast<void *>(part_o) : p.out;
+    a.sinks = p.sinks; a.error_flag = err_flag;
+    a.out_dtype = n_ksplit > 1 ? kDtypeF32 : p.out_dtype;
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
-    const int n_units = ((T + kCtaPos - 1) / kCtaPos) * kNHeadKv;
+    a.n_ksplit = n_ksplit; a.t_pad = t_pad; a.part_ml = part_ml;
+    const int n_units = n_units_q * n_ksplit;
     const dim3 grid(n_units < g_sm_count ? n_units : g_sm_count);
     a.n_units = n_units;
     static const bool round_robin = [] {
@@ -842,10 +916,15 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     }
     if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
     k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
-    if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*n_launches)++;
+    if (n_ksplit > 1) {
+        k_prefill_merge<<<unsigned(T) * (kNHead / 4), 128, 0, stream>>>(part_o, part_ml, p.out, p.out_dtype, T, t_pad, n_ksplit);
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+        (*n_launches)++;
+    }
+    if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
     return cudaSuccess;
 }
 

@@ -142,6 +142,40 @@ def test_long_prompt_on_a_full_layer_in_two_chunks(fa, fo):
             assert np.array_equal(v_dev[:, p].reshape(-1), fo.to_f16_bits(vc[p])), p
 
 
+def test_short_chunks_on_a_long_full_layer_history_split_their_key_range(fa, fo):
+    """The reference's own call pattern (chunks of at most 512 tokens, src/engine.mm:1080) on a full-attention layer
+    with a long history: such a launch has fewer work units than SMs, so the key range of every unit is split and
+    merged by log-sum-exp.  A 512-token chunk (2 ranges), a 100-token ragged chunk (8 ranges) and a 7-token chunk
+    after 4000 tokens of history; every output row of the short chunks against the oracle, fp32 and bf16 rows out."""
+    import torch
+
+    seed, hist = 8, 4000
+    chunks = [512, 100, 7]
+    T = hist + sum(chunks)
+    w = fo.layer_weights(seed, 0)
+    qkv, bits = bf16_round_rows(fo.raw_qkv(seed, 0, 0, T))
+    with _open(fa, "full_rope", T + 8) as h:
+        h.set_layer(0, *w)
+        out = np.zeros((T, 4096), np.float32)
+        h.prefill(0, 0, hist, bits[:hist], fa.BF16, out[:hist], fa.F32)
+        assert h.advance([0], hist) == 0
+        p = hist
+        out16 = np.zeros((chunks[0], 4096), np.uint16)
+        for i, n in enumerate(chunks):
+            rows = np.ascontiguousarray(bits[p:p + n])
+            if i == 0:  # the same chunk once more with bf16 rows out (the position has not moved yet)
+                h.prefill(0, 0, n, rows, fa.BF16, out16, fa.BF16)
+            h.prefill(0, 0, n, rows, fa.BF16, out[p:p + n], fa.F32)
+            assert h.advance([0], n) == 0
+            p += n
+        assert np.isfinite(out).all()
+        some = list(range(hist, hist + 40)) + list(range(hist + 480, T))
+        want, _, _ = oracle_at_positions(qkv, w, False, True, some)
+        assert_close(out[some], want, "split key range vs oracle")
+        got16 = fo.from_bf16_bits(out16)
+        assert np.abs(got16 - out[hist:hist + chunks[0]]).max() <= np.abs(out).max() * 2 ** -8
+
+
 @pytest.mark.parametrize("kind", ["swa_rope", "full_rope"])
 def test_prefill_then_decode_equals_decode_only(fa, fo, kind):
     """The reference's check-prefill idea (src/main.mm:317-346) at the kernel level: prefill the first part, decode the
