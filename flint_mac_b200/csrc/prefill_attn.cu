@@ -7,7 +7,8 @@
 // before P.V (prefill.metal:223), fp32 scores / statistics / accumulators.
 //
 // Shape chosen for B200: one CTA owns 128 query rows = 16 consecutive positions x the 8 query heads of one KV head,
-// so one K/V tile serves the whole GQA group and the key band of a CTA is 512+16 keys wide instead of 512+128.
+// so one K/V tile serves the whole GQA group and the key band of a Q tile is 512+16 keys wide instead of 512+128;
+// a CTA works on two such Q tiles (32 positions) that share every K/V tile.
 // Q, K and V tiles arrive by TMA (128-byte swizzle, no multicast) from half-precision staging written by the
 // prologue; S = Q.K^T and O += P.V run on the 5th-generation tensor core (tcgen05.mma, kind::f16) with both
 // accumulators in tensor memory; each thread owns one query row of S (tcgen05.ld 32x32b), so the softmax needs no
@@ -39,7 +40,7 @@ constexpr int kCtaPos = kQPos * kQTiles;  // 32 query positions per CTA
 constexpr int kBN = 128;               // keys per tile: an MMA narrower than N = 128 runs at half rate
 constexpr int kSlots = 3;              // ring of 32 KiB tile slots, used alternately for K and V tiles
 constexpr int kHist = kNSwa - 1;       // 512 keys of history a sliding-window query can see
-// Tensor memory (all 512 columns): scores S per Q tile (P, as halves, is written over the first half of S) and the
+// Tensor memory (all 512 columns): scores S per Q tile (read into registers, then free for the next tile's scores) and the
 // output accumulators.
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;               // + 128 * tile
@@ -216,7 +217,7 @@ enum {
     kBarQFull = kBarSlotEmpty + kSlots,     // [2] TMA -> MMA warp: the Q tile of the unit is in shared memory
     kBarQEmpty = kBarQFull + 2,             // [2] tensor core -> TMA warp: the unit's last Q.K^T of this Q tile is done
     kBarSReady = kBarQEmpty + 2,            // [2] tensor core -> softmax warps: S = Q.K^T of the current tile
-    kBarPReady = kBarSReady + 2,            // [2] softmax warps -> MMA warp: P is in tensor memory, S consumed (128 arrivals)
+    kBarPReady = kBarSReady + 2,            // [2] softmax warps -> MMA warp: P is in its shared-memory tile (128 arrivals)
     kBarPvDone = kBarPReady + 2,            // [2] tensor core -> softmax warps: O += P.V of the current tile
     kBarOFree = kBarPvDone + 2,             // [2] softmax warps -> MMA warp: O of the finished unit has been read out (128)
     kBarSFree = kBarOFree + 2,              // [2] softmax warps -> MMA warp: S of the current tile is in registers (128)
@@ -277,8 +278,9 @@ __device__ __forceinline__ int unit_at(const PfArgs &a, const int *local, int i)
 // tiles with TMA (K and V alternate through a ring of three 32 KiB slots); warp 9 issues every tcgen05.mma.  The two
 // Q tiles share each K/V tile and alternate on the tensor core: while one tile's warps run the softmax of a key tile,
 // the tensor core does P.V and the next Q.K^T of the other -- across unit boundaries too, so the start-up of a unit
-// (Q load, first scores) and the drain of the previous one (O / l, TMA store) overlap.  P.V takes P from tensor
-// memory; every product is 128 wide (N = 128; narrower MMAs run at half rate).
+// (Q load, first scores) and the drain of the previous one (O / l, TMA store) overlap.  P goes through shared memory
+// (so the next scores can be computed while the softmax runs); every product is 128 wide (N = 128; narrower MMAs
+// run at half rate).
 __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_v,
