@@ -232,6 +232,27 @@ class Attn:
         self._call("flint_attn_decode_dev", layer, len(seqs), _i32(seqs), _ptr(qkv_dev), qkv_dtype, _ptr(out_dev),
                    out_dtype, stream)
 
+    def prepared_decode_dev(self, layer, seqs, qkv_dtype, out_dev, out_dtype, stream: int = 0):
+        """For a caller that decodes the same batch every step (a serving loop): every argument except the address
+        of the step's q|k|v rows is converted once.  Returns f(qkv_address) that enqueues flint_attn_decode_dev."""
+        fn, h, n, arr, outp, err = self._lib.flint_attn_decode_dev, self._h, len(seqs), _i32(seqs), _ptr(out_dev), self._err
+
+        def call(qkv_address: int):
+            if fn(h, layer, n, arr, qkv_address, qkv_dtype, outp, out_dtype, stream, err, ERR_LEN) != 0:
+                raise FlintAttnError(err.value.decode(errors="replace"))
+
+        return call
+
+    def prepared_advance(self, seqs, n_tokens: int = 1):
+        """f() that advances the given sequences by n_tokens, with the index list converted once."""
+        fn, h, n, arr = self._lib.flint_attn_advance, self._h, len(seqs), _i32(seqs)
+
+        def call():
+            if fn(h, n, arr, n_tokens) != 0:
+                raise FlintAttnError("advance failed: a sequence would pass the end of the context")
+
+        return call
+
     def decode_partial_dev(self, layer, seqs, qkv_dev, qkv_dtype, partial_dev, stream: int = 0):
         self._call("flint_attn_decode_partial_dev", layer, len(seqs), _i32(seqs), _ptr(qkv_dev), qkv_dtype,
                    _ptr(partial_dev), stream)

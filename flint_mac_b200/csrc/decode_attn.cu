@@ -35,25 +35,6 @@ constexpr int kTileBytes = kTileKeys * kRowBytes;   // 16 KiB per K or V tile
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
-// Debug timeline (only with -DFLINT_DEC_TRACE): per CTA, clock64 at up to 12 points plus %globaltimer at entry/exit.
-#ifdef FLINT_DEC_TRACE
-constexpr int kTraceCtas = 1024, kTraceSlots = 16;
-__device__ long long g_dec_trace[kTraceCtas * kTraceSlots];
-__device__ __forceinline__ long long global_ns() {
-    long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
-    return t;
-}
-#define DEC_TRACE(slot)                                                                              \
-    do {                                                                                             \
-        if (threadIdx.x == 0 && blockIdx.x < kTraceCtas) {                                           \
-            g_dec_trace[blockIdx.x * kTraceSlots + (slot)] = (slot) >= 12 ? global_ns() : clock64(); \
-        }                                                                                            \
-    } while (0)
-#else
-#define DEC_TRACE(slot) do { } while (0)
-#endif
-
 template <int kStages>
 struct __align__(16) DecSmem {
     unsigned char k[kStages][kTileBytes];
@@ -214,8 +195,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     const int j0 = it.j0, j1 = it.j1;
     const int j_end = j1 + (it.fold ? 1 : 0);  // the new token sits right after the cached range of a fold item
     const int n_tiles = (j_end - j0 + kTileKeys - 1) / kTileKeys;
-    DEC_TRACE(12);
-    DEC_TRACE(0);
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     // layout of the merge steps at the end: 16 threads per head, 8 dims per thread; the head's sink is fetched now
     const int mh = tid >> 4, md = (tid & 15) * 8;
@@ -274,7 +253,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         if (t < n_tiles) load_tile(t);
         cp_async_commit();
     }
-    DEC_TRACE(1);
 
     {
         const float qscale = rsqrtf(float(kHeadDim)) * kLog2e;  // softmax runs in base 2
@@ -304,7 +282,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         }
     }
     __syncthreads();
-    DEC_TRACE(2);
 
     // B fragments of Q^T for the 8 k-steps: b0 = Q[head g][16k + 2t, +1], b1 = Q[head g][16k + 8 + 2t, +1]
     uint32_t bq[8][2];
@@ -391,7 +368,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with the tiles: the K tiles become the merge buffer
-    DEC_TRACE(3);
 
     // ---- merge the four warps --------------------------------------------------------------------------------
 #pragma unroll
@@ -458,10 +434,8 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
             if (md == 0) { rec[kHeadDim] = M * kLn2; rec[kHeadDim + 1] = L; }
         }
     }
-    DEC_TRACE(4);
     if (direct) {
         publish_group(p, tid);
-        DEC_TRACE(13);
         return;
     }
 
@@ -484,8 +458,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         sm.is_last = last;
     }
     __syncthreads();
-    DEC_TRACE(5);
-    DEC_TRACE(13);
     if (!sm.is_last) return;
 
     // One copy of the merge code serves both levels (see merge_records on code size).
@@ -511,8 +483,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
             sm.is_last = last;
         }
         __syncthreads();
-        DEC_TRACE(6);
-        DEC_TRACE(13);
         if (!sm.is_last) return;
         src = p.scratch2 + (size_t(it.sub0) * kGqa + mh) * kRecStride;
         n_src = n_sub;
@@ -532,8 +502,6 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         }
         publish_group(p, tid);
     }
-    DEC_TRACE(7);
-    DEC_TRACE(13);
 }
 
 // The work list either sits in device memory (any length) or, when it is short enough, travels in the kernel's
@@ -677,17 +645,5 @@ cudaError_t launch_combine(const CombineParams &p, cudaStream_t stream) {
     k_combine_parts<<<p.n * kNHead, kHeadDim, 0, stream>>>(p);
     return cudaGetLastError();
 }
-
-#ifdef FLINT_DEC_TRACE
-extern "C" int flint_dec_trace_read(long long *out, int clear) {
-    if (cudaMemcpyFromSymbol(out, g_dec_trace, sizeof(long long) * kTraceCtas * kTraceSlots) != cudaSuccess) return -1;
-    if (clear) {
-        void *ptr = nullptr;
-        if (cudaGetSymbolAddress(&ptr, g_dec_trace) != cudaSuccess) return -1;
-        cudaMemset(ptr, 0, sizeof(long long) * kTraceCtas * kTraceSlots);
-    }
-    return 0;
-}
-#endif
 
 }  // namespace flint

@@ -10,7 +10,10 @@
 // counters and the RoPE frequency table -- lives in the fixed array below, which is part of the loaded library
 // image on every GPU that loads it (about 10 MiB per GPU until the process exits).
 //
-// It runs the same kernel as flint_attn_decode_dev (k_decode_attn), with the same planner.
+// It runs the same kernel as flint_attn_decode_dev (k_decode_attn), with the same planner and the same choice of
+// kernel variant: a work list of up to 640 items travels in the kernel's parameters (no copy at all in front of the
+// launch); only a longer list is uploaded into the fixed array from a pageable host buffer, a copy for which the
+// runtime blocks the calling thread until the bytes are staged.
 #include <climits>
 #include <cmath>
 #include <cstdio>
@@ -25,7 +28,6 @@ namespace {
 
 constexpr int kMaxTokens = FLINT_ATTN_NOALLOC_MAX_TOKENS;  // 64
 constexpr int kMaxItems = FLINT_ATTN_NOALLOC_MAX_ITEMS;    // 2048
-constexpr int kTargetItems = 296;                          // what the handle uses on a 148-SM part
 
 // Layout of the fixed scratch (byte offsets, each a multiple of 256).  A group of n splits is merged in runs of
 // kMergeFan, so it needs ceil(n / kMergeFan) run counters / second-level records: at most kMaxRuns in total.
@@ -48,6 +50,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
 struct DeviceState {
     bool ready = false;
     unsigned char *base = nullptr;  // device address of g_noalloc_scratch on this GPU
+    int sm_count = 148;
 };
 DeviceState g_state[64];
 DecItem g_items_host[kMaxItems];  // staging for the work list; pageable on purpose (no cudaMallocHost)
@@ -75,6 +78,8 @@ const char *setup_device(int dev) {
     if (cudaMemset(base + kOffTickets, 0, kTicketBytes) != cudaSuccess)
         return "could not clear the arrival counters in the fixed scratch array";
     if (decode_kernel_setup() != cudaSuccess) return "could not set the decode kernel's shared-memory size";
+    if (cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        return "could not read the device's SM count";
     if (cudaDeviceSynchronize() != cudaSuccess) return "device error during set-up";
     st.base = base;
     st.ready = true;
@@ -114,8 +119,12 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
             return -1;
         }
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) {
         fail(err, err_len, "flint_attn_decode_noalloc_dev: no current CUDA device");
+        return -1;
+    }
+    if (dev >= int(sizeof(g_state) / sizeof(g_state[0]))) {
+        fail(err, err_len, "flint_attn_decode_noalloc_dev: device ordinals above 63 are not supported");
         return -1;
     }
     if (!g_state[dev].ready) {
@@ -125,7 +134,8 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
         }
     }
     // Same planner as the handle-based path; it reports -1 when the work list would not fit.
-    const int n_items = flint_attn_plan_decode(n, pos, is_swa, 0, is_swa ? INT32_MAX : n_slots, kTargetItems, g_plan,
+    const int target_items = 2 * g_state[dev].sm_count;  // one wave of two CTAs per SM, as the handle plans
+    const int n_items = flint_attn_plan_decode(n, pos, is_swa, 0, is_swa ? INT32_MAX : n_slots, target_items, g_plan,
                                                kMaxItems);
     if (n_items < 0) {
         snprintf(msg, sizeof(msg), "flint_attn_decode_noalloc_dev: the split-K work list exceeds the fixed scratch (%d items)",
@@ -153,19 +163,22 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
     }
     unsigned char *base = g_state[dev].base;
     cudaStream_t st = cudaStream_t(cuda_stream);
-    // Pageable source: the runtime has staged the bytes by the time this returns, so the host array can be reused.
-    if (cudaMemcpyAsync(base + kOffItems, g_items_host, sizeof(DecItem) * size_t(n_items), cudaMemcpyHostToDevice, st) !=
-        cudaSuccess) {
-        fail(err, err_len, "flint_attn_decode_noalloc_dev: work-list upload failed");
-        return -1;
-    }
     // The counters must start at zero.  The kernel leaves them at zero, but a launch that failed part-way would not.
     if (cudaMemsetAsync(base + kOffTickets, 0, kTicketBytes, st) != cudaSuccess) {
         fail(err, err_len, "flint_attn_decode_noalloc_dev: could not clear the arrival counters");
         return -1;
     }
     DecParams dp{};
-    dp.items = reinterpret_cast<const DecItem *>(base + kOffItems);
+    const bool inline_items = n_items <= kMaxParamItems;
+    if (!inline_items) {
+        // Pageable source: the runtime has staged the bytes by the time this returns, so the host array can be reused.
+        if (cudaMemcpyAsync(base + kOffItems, g_items_host, sizeof(DecItem) * size_t(n_items), cudaMemcpyHostToDevice,
+                            st) != cudaSuccess) {
+            fail(err, err_len, "flint_attn_decode_noalloc_dev: work-list upload failed");
+            return -1;
+        }
+    }
+    dp.items = inline_items ? nullptr : reinterpret_cast<const DecItem *>(base + kOffItems);
     dp.qkv = qkv_dev;
     dp.out = out_dev;
     dp.partial_out = nullptr;
@@ -184,7 +197,8 @@ extern "C" int32_t flint_attn_decode_noalloc_dev(int32_t n, const int32_t *pos, 
     dp.has_rope = has_rope;
     dp.qkv_dtype = qkv_dtype; dp.out_dtype = out_dtype;
     dp.mode = 0;
-    const cudaError_t e = launch_decode(dp, n_items, st);
+    const cudaError_t e = inline_items ? launch_decode_inline(dp, g_items_host, n_items, g_state[dev].sm_count, st)
+                                       : launch_decode(dp, n_items, st);
     if (e != cudaSuccess) {
         snprintf(msg, sizeof(msg), "flint_attn_decode_noalloc_dev: launch failed: %s", cudaGetErrorString(e));
         fail(err, err_len, msg);

@@ -59,6 +59,19 @@ struct PlanScratch {
     std::vector<uint64_t> keys;
 };
 
+// The last work list of a layer, kept so that the usual next call -- the same batch, every position advanced by one
+// -- is a patch of a few fields per item instead of a new plan (the planner is most of the host time of a call).
+// A patched list keeps the split structure of the plan it came from, so it is rebuilt from scratch every kPlanMaxAge
+// steps; by then a range has grown by at most one 64-key tile.
+constexpr int kPlanMaxAge = 64;
+constexpr int kPlanWays = 4;  // batches remembered per layer (a server may alternate between a few fixed batches)
+struct PlanCache {
+    bool valid = false;
+    int target_items = 0, n_groups = 0, n_records = 0, n_subs = 0, age = 0;
+    std::vector<int32_t> seqs, pos;
+    std::vector<DecItem> items;
+};
+
 void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi, int target_items,
                  std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs, PlanScratch &ps) {
     long long total = 0;
@@ -129,6 +142,34 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
     for (size_t i = 0; i < m; i++) items[i] = ps.gen[uint32_t(ps.keys[i])];
 }
 
+// Brings a cached work list to the positions `pos` when they equal the cached ones or are all one ahead, and nothing
+// about who folds the new token changed.  Returns false when the list has to be planned again.
+bool patch_plan(PlanCache &pc, int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi,
+                int target_items) {
+    if (!pc.valid || pc.target_items != target_items || int(pc.pos.size()) != n) return false;
+    if (memcmp(pc.seqs.data(), seqs, sizeof(int32_t) * size_t(n)) != 0) return false;
+    const int d = n > 0 ? pos[0] - pc.pos[0] : 0;
+    if (d != 0 && d != 1) return false;
+    for (int i = 0; i < n; i++) {
+        if (pos[i] - pc.pos[i] != d) return false;
+        if ((kv_lo <= pos[i] && pos[i] < kv_hi) != (kv_lo <= pc.pos[i] && pc.pos[i] < kv_hi)) return false;
+    }
+    if (d == 0) return true;
+    if (pc.age + 1 >= kPlanMaxAge) return false;
+    pc.age++;
+    for (DecItem &it : pc.items) {
+        const int p = pos[it.tok];
+        it.pos = p;
+        if (it.split != it.n_split - 1) continue;  // only the last range of a group ends at the position
+        const int kb = is_swa ? std::max(p - (kNSwa - 1), 0) : 0;
+        const int lo = std::min(std::max(kb, kv_lo), p);
+        if (it.n_split == 1) it.j0 = lo;  // a sliding window moves with the position (windows are never split)
+        it.j1 = std::max(it.j0, std::min(p, kv_hi));
+    }
+    memcpy(pc.pos.data(), pos, sizeof(int32_t) * size_t(n));
+    return true;
+}
+
 }  // namespace
 
 struct flint_attn {
@@ -152,7 +193,8 @@ struct flint_attn {
     size_t io_cap = 0;
     PrefillWorkspace pf;
     int64_t launches = 0;
-    std::vector<DecItem> items;
+    std::vector<PlanCache> plan_cache;  // kPlanWays per layer
+    std::vector<int> plan_victim;       // per layer: the way the next unknown batch replaces
     PlanScratch plan_scratch;
     std::vector<int32_t> batch_pos;
     std::vector<uint32_t> seen;  // per sequence: the number of the last decode batch it appeared in
@@ -225,7 +267,7 @@ struct flint_attn {
     }
 
     // Upload a work list through the pinned ring; returns the device copy, valid for the next launch on `st`.
-    const DecItem *upload_items(cudaStream_t st) {
+    const DecItem *upload_items(const std::vector<DecItem> &items, cudaStream_t st) {
         const int r = ring_next;
         ring_next = (ring_next + 1) % kRing;
         CK(cudaEventSynchronize(ring_ev[r]));  // the launch that last used this slot has consumed it
@@ -275,9 +317,17 @@ struct flint_attn {
         }
     }
 
-    // mode 0: out [n][4096]; mode 1: partial_out [n][32][130]
+    // Rows of a host-buffer call.  `mapped` is the device address of the caller's page-locked rows (null if they
+    // are pageable): the kernel then reads them in place; otherwise they are copied to `staging` first.
+    struct HostRows {
+        const void *host = nullptr, *mapped = nullptr;
+        void *staging = nullptr;
+        size_t bytes = 0;
+    };
+
+    // mode 0: out [n][4096]; mode 1: partial_out [n][32][130]; mode 2: records to every peer's gather buffer
     void decode_dev(int il, int n, const int32_t *seqs, const void *qkv, int qkv_dtype, void *out, int out_dtype,
-                    float *partial_out, int mode, cudaStream_t st) {
+                    float *partial_out, int mode, cudaStream_t st, uint32_t step = 0, const HostRows *rows = nullptr) {
         CK(cudaSetDevice(device));
         Layer &L = layer(il);
         check_seqs(n, seqs);
@@ -298,13 +348,48 @@ struct flint_attn {
             if (seen[seqs[i]] == batch_no) throw std::runtime_error("a sequence appears twice in one decode batch");
             seen[seqs[i]] = batch_no;
         }
-        int n_groups = 0, n_records = 0, n_subs = 0;
-        plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, items, n_groups, n_records, n_subs,
-                    plan_scratch);
+        PlanCache *hit = nullptr;
+        for (int w = 0; w < kPlanWays && !hit; w++) {
+            PlanCache &c = plan_cache[size_t(il) * kPlanWays + w];
+            if (c.valid && int(c.seqs.size()) == n && c.seqs[0] == seqs[0] &&
+                patch_plan(c, n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items))
+                hit = &c;
+        }
+        if (!hit) {
+            // replace the way that holds this batch at other positions, else the next victim
+            int way = -1;
+            for (int w = 0; w < kPlanWays && way < 0; w++) {
+                const PlanCache &c = plan_cache[size_t(il) * kPlanWays + w];
+                if (c.valid && int(c.seqs.size()) == n && memcmp(c.seqs.data(), seqs, sizeof(int32_t) * size_t(n)) == 0) way = w;
+            }
+            if (way < 0) way = plan_victim[il] = (plan_victim[il] + 1) % kPlanWays;
+            hit = &plan_cache[size_t(il) * kPlanWays + way];
+            hit->valid = false;
+            plan_decode(n, seqs, p.data(), L.is_swa, L.kv_lo, L.kv_hi, target_items, hit->items, hit->n_groups,
+                        hit->n_records, hit->n_subs, plan_scratch);
+            hit->seqs.assign(seqs, seqs + n);
+            hit->pos.assign(p.begin(), p.end());
+            hit->target_items = target_items;
+            hit->age = 0;
+            hit->valid = true;
+        }
+        PlanCache &pc = *hit;
+        const std::vector<DecItem> &items = pc.items;
+        const int n_groups = pc.n_groups, n_records = pc.n_records, n_subs = pc.n_subs;
+        if (rows) {
+            // Page-locked rows are read by the kernel where they lie (each CTA fetches the 2-4 KB it needs over PCIe
+            // behind its first K/V tiles) unless the groups are cut into many ranges, each of which would fetch the
+            // same rows again; then, and for pageable rows, one copy brings them to the device first.
+            if (rows->mapped && items.size() <= 2 * size_t(n_groups)) qkv = rows->mapped;
+            else {
+                CK(cudaMemcpyAsync(rows->staging, rows->host, rows->bytes, cudaMemcpyHostToDevice, st));
+                qkv = rows->staging;
+            }
+        }
         ensure_scratch(n_records, n_subs, n_groups);
         const bool inline_items = items.size() <= size_t(kMaxParamItems);
         DecParams dp{};
-        dp.items = inline_items ? nullptr : upload_items(st);
+        dp.items = inline_items ? nullptr : upload_items(items, st);
         dp.qkv = qkv;
         dp.out = out;
         dp.partial_out = partial_out;
@@ -321,14 +406,14 @@ struct flint_attn {
         dp.mode = mode;
         if (mode == 2) {
             const size_t rec_bytes = size_t(xchg_n) * kNHead * kPartialDim * sizeof(float);
-            const size_t buf_off = 256 + size_t(xchg_step & 1) * kv_ranks * rec_bytes + size_t(kv_rank) * rec_bytes;
+            const size_t buf_off = 256 + size_t(step & 1) * kv_ranks * rec_bytes + size_t(kv_rank) * rec_bytes;
             for (int r = 0; r < kv_ranks; r++) {
                 dp.peer_out[r] = reinterpret_cast<float *>(xchg_peer[r] + buf_off);
                 dp.peer_flag[r] = reinterpret_cast<uint32_t *>(xchg_peer[r]);
             }
             dp.n_peers = kv_ranks;
             dp.rank = kv_rank;
-            dp.step = xchg_step;
+            dp.step = step;
             dp.groups_done = reinterpret_cast<int *>(xchg + (kMaxPeers + 1) * sizeof(uint32_t));
             dp.n_groups = n_groups;
         }
@@ -388,6 +473,8 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
         CK(cudaMemcpy(a->inv_freq, freq, sizeof(freq), cudaMemcpyHostToDevice));
         const int shard = (cfg->n_ctx + ranks - 1) / ranks;
         a->layers.resize(cfg->n_layers);
+        a->plan_cache.resize(size_t(cfg->n_layers) * kPlanWays);
+        a->plan_victim.assign(cfg->n_layers, 0);
         for (int il = 0; il < cfg->n_layers; il++) {
             Layer &L = a->layers[il];
             L.is_swa = cfg->layer_is_swa[il] != 0;
@@ -552,8 +639,11 @@ int32_t flint_attn_decode_xchg_post_dev(flint_attn *a, int32_t layer, int32_t n,
         if (!a->xchg_peer[r]) throw std::runtime_error("exchange buffer not connected to every rank");
     if (n > a->xchg_n) throw std::runtime_error("batch larger than the exchange buffer");
     if (a->layer(layer).is_swa) throw std::runtime_error("sliding-window layers are not sharded: use decode_dev");
-    a->xchg_step++;
-    a->decode_dev(layer, n, seqs, qkv_dev, qkv_dtype, nullptr, 0, nullptr, 2, cudaStream_t(cuda_stream));
+    // The step counter moves only once the launch is enqueued: a call that fails validation (context full, a
+    // duplicate sequence, a CUDA error) must leave this rank on the step its peers expect next.
+    const uint32_t step = a->xchg_step + 1;
+    a->decode_dev(layer, n, seqs, qkv_dev, qkv_dtype, nullptr, 0, nullptr, 2, cudaStream_t(cuda_stream), step);
+    a->xchg_step = step;
     return 0;
     API_CATCH(-1)
 }
@@ -612,17 +702,25 @@ int32_t flint_attn_decode(flint_attn *a, int32_t layer, int32_t n, const int32_t
     const size_t out_bytes = size_t(n) * kQDim * elem_size(out_dtype);
     a->ensure_io(in_pad + out_bytes);
     char *d_in = static_cast<char *>(a->io_dev), *d_out = d_in + in_pad;
-    // Output rows in page-locked host memory are written by the kernel itself (posted writes over PCIe that overlap
-    // the kernel's tail) instead of being staged on the device and copied back.
-    void *out_mapped = nullptr;
-    cudaPointerAttributes attr{};
-    if (cudaPointerGetAttributes(&attr, out) == cudaSuccess && attr.type == cudaMemoryTypeHost && attr.devicePointer &&
-        (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15) == 0)
-        out_mapped = attr.devicePointer;
-    else
+    // Rows in page-locked host memory are accessed by the kernel itself: output rows are posted writes over PCIe
+    // that overlap the kernel's tail, input rows are fetched by the CTAs that need them.  Pageable rows go through
+    // a device staging buffer and a copy each way.
+    auto mapped_address = [](const void *host) -> void * {
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, host) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+            attr.devicePointer && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15) == 0)
+            return attr.devicePointer;
         cudaGetLastError();  // pageable memory makes the query fail on some drivers: not an error here
-    CK(cudaMemcpyAsync(d_in, qkv, in_bytes, cudaMemcpyHostToDevice, a->stream));
-    a->decode_dev(layer, n, seqs, d_in, qkv_dtype, out_mapped ? out_mapped : d_out, out_dtype, nullptr, 0, a->stream);
+        return nullptr;
+    };
+    void *out_mapped = mapped_address(out);
+    flint_attn::HostRows rows;
+    rows.host = qkv;
+    rows.mapped = mapped_address(qkv);
+    rows.staging = d_in;
+    rows.bytes = in_bytes;
+    a->decode_dev(layer, n, seqs, d_in, qkv_dtype, out_mapped ? out_mapped : d_out, out_dtype, nullptr, 0, a->stream, 0,
+                  &rows);
     if (!out_mapped) CK(cudaMemcpyAsync(out, d_out, out_bytes, cudaMemcpyDeviceToHost, a->stream));
     CK(cudaStreamSynchronize(a->stream));  // synchronous like the reference (src/engine.mm:930)
     return 0;
@@ -694,12 +792,18 @@ int32_t flint_attn_check(flint_attn *a, char *err, int32_t err_len) {
     API_TRY
     CK(cudaSetDevice(a->device));
     CK(cudaDeviceSynchronize());
+    // Each device error word is reported once and cleared, the way the reference raises once per failed command
+    // buffer (src/engine.mm:930-932): later, healthy launches on this handle are not failed by an old error.
     int flag = 0;
     CK(prefill_error_flag(a->pf, &flag));
     if (flag) throw std::runtime_error("prefill kernel reported device error " + std::to_string(flag));
     if (a->xchg) {
-        CK(cudaMemcpy(&flag, a->xchg + kMaxPeers * sizeof(uint32_t), sizeof(int), cudaMemcpyDeviceToHost));
-        if (flag) throw std::runtime_error("the wait for a peer's partial records ran out (exchange error " + std::to_string(flag) + ")");
+        int *word = reinterpret_cast<int *>(a->xchg + kMaxPeers * sizeof(uint32_t));
+        CK(cudaMemcpy(&flag, word, sizeof(int), cudaMemcpyDeviceToHost));
+        if (flag) {
+            CK(cudaMemset(word, 0, sizeof(int)));
+            throw std::runtime_error("the wait for a peer's partial records ran out (exchange error " + std::to_string(flag) + ")");
+        }
     }
     return 0;
     API_CATCH(-1)

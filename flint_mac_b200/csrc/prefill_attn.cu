@@ -63,14 +63,7 @@ constexpr int kSchedLocal = 640;
 constexpr int kSmemBytes = kOffSched + kSchedLocal * 4;  // 232192 B: one CTA per SM
 static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 
-#ifdef FLINT_PF_TRACE
-#define PF_TRACE(slot) do { if (a.trace && blockIdx.x == 60) a.trace[(slot)] = clock64(); } while (0)
-#else
-#define PF_TRACE(slot) do { } while (0)
-#endif
-
 struct PfArgs {
-    long long *trace;  // debug timeline (only with FLINT_PF_TRACE)
     const int *sched;  // [n_rounds][gridDim.x] unit of CTA b in its round i, -1 = none; nullptr: round-robin
     int n_rounds, n_units;
     const __half *q_st;  // [32][n_tok][128] normalised, rotated, pre-scaled queries
@@ -180,8 +173,12 @@ __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) 
         const bool is_k = i < kNHeadKv;
         const int kvh = i & (kNHeadKv - 1);
         const float4 y = is_k ? pf_norm_rope(x[i], wk, cs, sn, lane, a.has_rope != 0) : x[i];
-        __half *cache = is_k ? a.k_cache : a.v_cache;
-        pf_store_half4(cache + (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane, y);
+        // On a ring layer tokens t and t + 1024 of one launch share a slot: only the last token that maps to a slot
+        // stores there, so the ring's final contents do not depend on the order in which the CTAs run.
+        if (!a.is_swa || t + kSwaRing >= a.n_tok) {
+            __half *cache = is_k ? a.k_cache : a.v_cache;
+            pf_store_half4(cache + (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane, y);
+        }
         if (a.k_st) {
             __half *st = is_k ? a.k_st : a.v_st;
             pf_store_half4(st + (size_t(kvh) * (a.n_hist + a.n_tok) + a.n_hist + t) * kHeadDim + 4 * lane, y);
@@ -297,7 +294,6 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
 
     const int tid = threadIdx.x, warp = tid >> 5;
-    if (tid == 0) PF_TRACE(999);
     int *sched_local = reinterpret_cast<int *>(gen + kOffSched);
     if (a.sched)
         for (int i = tid; i < min(a.n_rounds, kSchedLocal); i += kThreadsAttn)
@@ -444,14 +440,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 // computed while the softmax of the current tile runs; P.V follows when P has been written.
 #pragma unroll
                 for (int w = 0; w < kQTiles; w++) {
-                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w);
                     if (more) ok = ok && issue_qk(w, nxt);
-                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 1);
                 }
 #pragma unroll
                 for (int w = 0; w < kQTiles; w++) {
                     ok = ok && issue_pv(w, cur);
-                    if (leader) PF_TRACE(1000 + (cur.j & 63) * 8 + 4 * w + 2);
                 }
                 if (!more) break;
                 cur = nxt;
@@ -482,10 +475,8 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
         const bool has_sink = un.split == 0;
         float m = has_sink ? sink2 : -INFINITY, l = has_sink ? 1.0f : 0.0f;
         for (int kt = 0; kt < n_tiles && ok; kt++) {
-            if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 0);
             ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + w), j & 1));  // warp-uniform for tcgen05.ld
             if (!ok) break;
-            if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 1);
             tc5::fence_after_sync();
             const int kbase = klo + kt * kBN;
             const int n_cols = min(kBN, (n_keys - kt * kBN + 15) & ~15);  // columns the MMA wrote (same as the issuer)
@@ -601,7 +592,6 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tc5::fence_proxy_async();
             tc5::mbar_arrive(bar(kBarPReady + w));
-            if (r == 0) PF_TRACE(w * 400 + (j % 48) * 8 + 2);
             j++;
         }
         // ---- drain of the unit.  The scores of the last tile proved P.V of the tile before it done, so a parity wait
@@ -678,7 +668,6 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 }
             }
         }
-        if (r == 0) PF_TRACE(910 + w);
         }  // units
         if (!ok && (tid & 31) == 0) atomicExch(a.error_flag, 1);  // a wait ran out: report, then the normal teardown
         if (r == 0) tc5::tma_store_wait_read();                    // shared memory must outlive the last store's reads
@@ -725,9 +714,6 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 int g_sm_count = 148;
-#ifdef FLINT_PF_TRACE
-long long *g_trace_buf = nullptr;
-#endif
 
 // half tensor [n_outer][n_rows][128] viewed as 3-D {128, n_rows, n_outer}, box {64, box_rows, box_outer}
 cudaError_t make_map(CUtensorMap *map, const void *base, int n_rows, int n_outer, int box_rows, int box_outer) {
@@ -887,16 +873,6 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     if ((e = make_map(&tm_v, vb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
 
     PfArgs a{};
-    a.trace = nullptr;
-#ifdef FLINT_PF_TRACE
-    {
-        static long long *trace_buf = nullptr;  // debug builds only: 2048 slots, read back by the trace tool
-        if (!trace_buf) { cudaMalloc(&trace_buf, 2048 * sizeof(long long)); }
-        cudaMemsetAsync(trace_buf, 0, 2048 * sizeof(long long), stream);
-        a.trace = trace_buf;
-        g_trace_buf = trace_buf;
-    }
-#endif
     a.q_st = q_st;
     a.out = n_ksplit > 1 ? static_cast<void *>(part_o) : p.out;
     a.sinks = p.sinks; a.error_flag = err_flag;
@@ -930,17 +906,12 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     return cudaSuccess;
 }
 
-#ifdef FLINT_PF_TRACE
-extern "C" int flint_pf_trace_read(long long *out) {
-    if (!g_trace_buf) return -1;
-    return cudaMemcpy(out, g_trace_buf, 2048 * sizeof(long long), cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : -1;
-}
-#endif
-
 cudaError_t prefill_error_flag(const PrefillWorkspace &ws, int *flag) {
     *flag = 0;
     if (!ws.buf) return cudaSuccess;
-    return cudaMemcpy(flag, ws.buf, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaError_t e = cudaMemcpy(flag, ws.buf, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && *flag) e = cudaMemset(ws.buf, 0, sizeof(int));  // reported once, then cleared
+    return e;
 }
 
 }  // namespace flint

@@ -33,7 +33,7 @@ cudaError_t prefill_kernel_setup();
 cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStream_t stream, int *n_launches);
 void prefill_workspace_free(PrefillWorkspace &ws);
 // Reads the device-side error word of the last prefill launches (0 = none; 1 = a bounded wait ran out; 2 = shared
-// memory was not 1024-byte aligned).  Blocking.
+// memory was not 1024-byte aligned).  Blocking.  A non-zero word is cleared after it has been read.
 cudaError_t prefill_error_flag(const PrefillWorkspace &ws, int *flag);
 
 }  // namespace flint

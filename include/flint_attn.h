@@ -142,7 +142,7 @@ int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_
 
 /* Wait for everything this handle enqueued and report an asynchronous failure of the *_dev calls (a CUDA error,
  * or a kernel whose bounded wait ran out), in the way the reference turns cb.error into an exception after
- * waitUntilCompleted (src/engine.mm:930-932). */
+ * waitUntilCompleted (src/engine.mm:930-932).  A device-side error is reported by one call and cleared. */
 int32_t flint_attn_check(flint_attn *a, char *err, int32_t err_len);
 
 /* ---- cache access for tests and cache pre-loading (counterpart of the Engine::debug_* hooks, src/engine.h:37-47)
@@ -184,7 +184,9 @@ double flint_attn_kernel_ms(flint_attn *a, int64_t *n_timed);
  * GPU (the KV caches live there), a plug-in inside a framework that owns the allocator, or a latency-critical
  * section where a device allocation's implicit synchronisation is not acceptable.  The handle-based calls above
  * allocate (caches at open; scratch and staging on demand); this one calls no cudaMalloc / cudaFree /
- * cudaMallocHost and uses no handle.  Same kernel and same arithmetic as flint_attn_decode_dev.
+ * cudaMallocHost and uses no handle.  Same kernel, same planner, same kernel variants and same arithmetic as
+ * flint_attn_decode_dev.  "Allocates nothing" is about CUDA memory: the planner keeps its work list in
+ * thread-local host vectors that grow on the host heap the first time a thread plans a batch of a given size.
  *
  * The caller owns and passes everything as device pointers: qkv rows [n][5120], out rows [n][4096], the K and V
  * caches of the n sequences, half [n][4][n_slots][128] (row i of the batch uses cache i; n_slots = 1024 on a
@@ -196,6 +198,9 @@ double flint_attn_kernel_ms(flint_attn *a, int64_t *n_timed);
  *
  * The first call on each device resolves the array's device address, fills the RoPE table and clears the
  * counters with blocking operations on the default stream: make that first call before any stream capture begins.
+ * A work list of up to 640 items travels in the kernel's parameters; a longer one is uploaded from a pageable host
+ * buffer, which blocks the calling thread until the bytes are staged.  The positions are read on the host at call
+ * time: whatever replays the enqueued work later replays it for those positions.
  * All calls on a device share the one array, and it keeps the previous call's partial records: two calls that may
  * overlap on the GPU (different streams, or different host threads) race on it -- issue them on one stream or
  * order them yourself.  Host-side it is not re-entrant either. */

@@ -72,3 +72,14 @@ def oracle_at_positions(qkv: np.ndarray, weights, is_swa: bool, has_rope: bool, 
                            int(is_swa), att, 8)
         out[i] = att
     return out, kc, vc
+
+
+def device_view(torch, ptr: int, numel: int, dtype):
+    """A torch view (no copy) of device memory owned by the library, e.g. a layer's K or V cache."""
+    class _Holder:
+        pass
+
+    itemsize = torch.empty((), dtype=dtype).element_size()
+    holder = _Holder()
+    holder.__cuda_array_interface__ = {"shape": (numel * itemsize,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+    return torch.as_tensor(holder, device="cuda").view(dtype)

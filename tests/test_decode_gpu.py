@@ -4,7 +4,7 @@ import os
 import numpy as np
 import pytest
 
-from helpers import KINDS, assert_close, bf16_round_rows, synth_cache_f16, to_slot_layout
+from helpers import KINDS, assert_close, bf16_round_rows, device_view, synth_cache_f16, to_slot_layout
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
@@ -136,7 +136,7 @@ def test_split_invariance_and_sampled_oracle_at_config2_size(fa, fo):
         # fill the caches in place with N(0,1) halves (zero-copy views of the library's buffers)
         numel = B * 4 * n_slots * 128
         for ptr in (kptr, vptr):
-            buf = _as_tensor(torch, ptr, numel, torch.float16)
+            buf = device_view(torch, ptr, numel, torch.float16)
             buf.normal_(generator=gen)
         for s in range(B):
             h.set_pos(s, S)
@@ -156,17 +156,6 @@ def test_split_invariance_and_sampled_oracle_at_config2_size(fa, fo):
             # rewrites it with the same values
             want = fo.decode_token_f16cache(qkv_host[s], S, *w, False, True, k16, v16, n_threads=8)
             assert_close(outs[0][s], want, f"config-2 sequence {s}")
-
-
-def _as_tensor(torch, ptr, numel, dtype):
-    """A torch view of device memory owned by the library (no copy)."""
-    class _Holder:
-        pass
-
-    itemsize = torch.empty((), dtype=dtype).element_size()
-    holder = _Holder()
-    holder.__cuda_array_interface__ = {"shape": (numel * itemsize,), "typestr": "|u1", "data": (ptr, False), "version": 3}
-    return torch.as_tensor(holder, device="cuda").view(dtype)
 
 
 def test_kv_sharded_partials_and_combine(fa, fo):
@@ -272,6 +261,12 @@ def test_kv_sharded_exchange_through_peer_buffers(fa, fo):
     try:
         with pytest.raises(fa.FlintAttnError, match="nothing was posted"):
             handles[0].combine_xchg_dev(0, 1, torch.empty(1, 4096, device="cuda"), fa.F32)
+        # a post that fails validation must not move this rank's step counter (its peers would wait for a step that
+        # is never published)
+        handles[0].set_pos(0, n_ctx)
+        with pytest.raises(fa.FlintAttnError, match="context full"):
+            handles[0].decode_xchg_post_dev(0, [0], torch.zeros(1, 5120, device="cuda"), fa.F32)
+        handles[0].set_pos(0, P)
         outs = torch.zeros(2, steps, 4096, device="cuda")
         for s in range(steps):
             q_dev = torch.from_numpy(rows[s:s + 1]).cuda()
@@ -306,6 +301,7 @@ def test_exchange_wait_is_bounded(fa, fo):
         handles[0].combine_xchg_dev(0, 1, out, fa.F32)
         with pytest.raises(fa.FlintAttnError, match="ran out"):
             handles[0].check()
+        handles[0].check()  # reported once, then cleared: the handle is usable again
         torch.cuda.synchronize()
         assert float((out + 1).sum().item()) == 4096.0  # the device still answers; the output was left alone
     finally:

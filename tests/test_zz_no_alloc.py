@@ -52,10 +52,11 @@ def test_noalloc_decode_matches_handle_decode_twice_in_a_row(fo, kind):
             fa.decode_noalloc_dev(pos, qkv, fa.BF16, got, fa.F32, k_mine, v_mine, n_slots, is_swa, has_rope, qn_d, kn_d,
                                   sk_d)
             torch.cuda.synchronize()
-            # same kernel, same work list, same inputs: the tolerance of the other decode tests is far from needed
+            # Same kernel and same inputs.  The handle may cut the key ranges a little differently (on the second call
+            # it extends its previous work list by one position instead of planning anew), so the two agree to the
+            # tolerance of the split-invariance test rather than bit for bit.
             assert torch.isfinite(got).all()
-            assert (got - want).abs().max().item() <= 2e-3
-            assert torch.equal(got, want), f"call {call}: outputs differ from flint_attn_decode_dev"
+            assert (got - want).abs().max().item() <= 2e-5, f"call {call}: outputs differ from flint_attn_decode_dev"
             # both wrote the new token's K/V into its slot
             for s, p in enumerate(pos):
                 slot = fo.slot(p, is_swa)
