@@ -8,7 +8,8 @@ from typing import Sequence
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libflint_attn.so")
+# FLINT_ATTN_LIB names another build of the same library (an A/B comparison, a debug build)
+LIB_PATH = os.environ.get("FLINT_ATTN_LIB") or os.path.join(HERE, "libflint_attn.so")
 
 F32, BF16 = 0, 1
 N_HEAD, N_HEAD_KV, HEAD_DIM = 32, 4, 128

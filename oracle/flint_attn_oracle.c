@@ -273,6 +273,71 @@ void fo_combine(const float *part, int n_split, const float *sinks, float *out) 
 }
 
 /* ------------------------------------------------------------------ integer maps */
+/* ---- src/main.mm:253-305: the all-double statement with half-rounded K/V ------------------------------------ */
+static void norm_rope_double(const float *in, const float *w, int pos, int has_rope, double *o) { /* main.mm:253-266 */
+    double ss = 0;
+    for (int d = 0; d < FO_HEAD_DIM; d++) ss += (double)in[d] * in[d];
+    const double sc = 1.0 / sqrt(ss / FO_HEAD_DIM + FO_RMS_EPS);
+    double t[FO_HEAD_DIM];
+    for (int d = 0; d < FO_HEAD_DIM; d++) t[d] = in[d] * sc * w[d];
+    for (int d = 0; d < FO_HEAD_DIM; d++) o[d] = t[d];
+    if (!has_rope) return;
+    for (int i = 0; i < FO_HEAD_DIM / 2; i++) {
+        const double a = pos * pow((double)FO_ROPE_THETA, -2.0 * i / FO_HEAD_DIM), c = cos(a), s = sin(a);
+        o[i] = t[i] * c - t[i + 64] * s;
+        o[i + 64] = t[i] * s + t[i + 64] * c;
+    }
+}
+
+void fo_attend_double_f16(const float *qkv, int n, const float *q_norm, const float *k_norm, const float *sinks,
+                          int is_swa, int has_rope, const int32_t *probe_pos, int n_pos, const int32_t *probe_heads,
+                          int n_heads, double *out) {
+    const int QS = FO_QKV_DIM;
+    double *K = (double *)malloc(sizeof(double) * (size_t)n * FO_KV_DIM);
+    double *V = (double *)malloc(sizeof(double) * (size_t)n * FO_KV_DIM);
+    double *sc = (double *)malloc(sizeof(double) * (size_t)(n + 1));
+    /* all keys / values first, rounded through half (main.mm:268-278) */
+    for (int p = 0; p < n; p++)
+        for (int hk = 0; hk < FO_N_HEAD_KV; hk++) {
+            double tmp[FO_HEAD_DIM];
+            norm_rope_double(&qkv[(size_t)p * QS + FO_Q_DIM + hk * FO_HEAD_DIM], k_norm, p, has_rope, tmp);
+            for (int d = 0; d < FO_HEAD_DIM; d++) {
+                K[(size_t)p * FO_KV_DIM + hk * FO_HEAD_DIM + d] = (double)(_Float16)tmp[d];
+                V[(size_t)p * FO_KV_DIM + hk * FO_HEAD_DIM + d] =
+                    (double)(_Float16)qkv[(size_t)p * QS + FO_Q_DIM + FO_KV_DIM + hk * FO_HEAD_DIM + d];
+            }
+        }
+    for (int ip = 0; ip < n_pos; ip++)
+        for (int ih = 0; ih < n_heads; ih++) { /* main.mm:281-305 */
+            const int p = probe_pos[ip], h = probe_heads[ih];
+            double q[FO_HEAD_DIM];
+            norm_rope_double(&qkv[(size_t)p * QS + h * FO_HEAD_DIM], q_norm, p, has_rope, q);
+            const int kvh = h / FO_GQA, lo = is_swa ? (p - (FO_N_SWA - 1) > 0 ? p - (FO_N_SWA - 1) : 0) : 0;
+            double m = sinks[h], l = 0, acc[FO_HEAD_DIM];
+            for (int i = 0; i < FO_HEAD_DIM; i++) acc[i] = 0;
+            for (int j = lo; j <= p; j++) {
+                double d = 0;
+                for (int i = 0; i < FO_HEAD_DIM; i++) d += q[i] * K[(size_t)j * FO_KV_DIM + kvh * FO_HEAD_DIM + i];
+                sc[j] = d / sqrt((double)FO_HEAD_DIM);
+                m = m > sc[j] ? m : sc[j];
+            }
+            l = exp(sinks[h] - m);
+            for (int j = lo; j <= p; j++) {
+                const double w = exp(sc[j] - m);
+                l += w;
+                for (int i = 0; i < FO_HEAD_DIM; i++) acc[i] += w * V[(size_t)j * FO_KV_DIM + kvh * FO_HEAD_DIM + i];
+            }
+            for (int i = 0; i < FO_HEAD_DIM; i++) out[((size_t)ip * n_heads + ih) * FO_HEAD_DIM + i] = acc[i] / l;
+        }
+    free(K);
+    free(V);
+    free(sc);
+}
+
+void fo_gen_grid(uint64_t seed, uint64_t stream, uint64_t first, uint64_t n, float *out) { /* main.mm:247 */
+    for (uint64_t i = 0; i < n; i++) out[i] = ((int)(fo_gen_u64(seed, stream, first + i) % 2001) - 1000) / 500.0f;
+}
+
 int32_t fo_slot(int32_t pos, int is_swa) { return is_swa ? (pos & (FO_SWA_RING - 1)) : pos; }
 
 int32_t fo_k_begin(int32_t pos, int is_swa) {

@@ -98,6 +98,19 @@ void fo_attend_partial(const float *q, const float *kc, const float *vc, int j0,
  * part: [32][n_split][130]; out [32][128]. */
 void fo_combine(const float *part, int n_split, const float *sinks, float *out);
 
+/* The reference's second CPU statement of this path, the one its own attention unit test compares the GPU with
+ * (src/main.mm:253-305): everything in double -- RMSNorm, RoPE angles from pow/cos/sin in double, scores, a two-pass
+ * softmax with the sink -- with K (after norm/RoPE) and V rounded through IEEE half as the caches hold them.  In the
+ * reference a full-attention layer has no RoPE (src/main.mm:244,262); here the two flags stay separate.
+ * qkv: raw rows [n][5120] of positions 0..n-1.  For each of the n_pos probe positions and n_heads probe heads the
+ * attention output goes to out[(ip * n_heads + ih) * 128 ..] as double. */
+void fo_attend_double_f16(const float *qkv, int n, const float *q_norm, const float *k_norm, const float *sinks,
+                          int is_swa, int has_rope, const int32_t *probe_pos, int n_pos, const int32_t *probe_heads,
+                          int n_heads, double *out);
+/* Inputs of the kind that test draws, (rand() % 2001 - 1000) / 500 (src/main.mm:247): uniform on the grid
+ * {-2, -1.998, ..., 2}, here from the seeded generator (rand() itself is platform-specific). */
+void fo_gen_grid(uint64_t seed, uint64_t stream, uint64_t first, uint64_t n, float *out);
+
 /* ---- integer maps (bit-exact items) ------------------------------------------ */
 /* src/metal/fused.metal:269-274, prefill.metal:106 */
 int32_t fo_slot(int32_t pos, int is_swa);

@@ -62,6 +62,9 @@ def lib():
                                                C.c_int64, _f32p, C.c_int]
         L.fo_attend_partial.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, _f32p]
         L.fo_combine.argtypes = [_f32p, C.c_int, _f32p, _f32p]
+        L.fo_attend_double_f16.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, _i32p, C.c_int, _i32p,
+                                           C.c_int, np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")]
+        L.fo_gen_grid.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _f32p]
         L.fo_slot.argtypes = [C.c_int32, C.c_int]
         L.fo_slot.restype = C.c_int32
         L.fo_k_begin.argtypes = [C.c_int32, C.c_int]
@@ -185,6 +188,30 @@ def decode_token_f16cache(qkv_row, pos: int, qn, kn, sinks, is_swa: bool, has_ro
     lib().fo_decode_token_f16cache(np.ascontiguousarray(qkv_row, np.float32), pos, qn, kn, sinks, int(is_swa),
                                    int(has_rope), k16.reshape(-1), v16.reshape(-1), n_slots, att, n_threads)
     return att
+
+
+# The probe set of the reference's own attention unit test (src/main.mm:280-281).
+PROBE_POS = (0, 1, 31, 32, 200, 511, 512, 513, 600, 1023, 1024, 1100, 1299)
+PROBE_HEADS = (0, 7, 8, 31)
+
+
+def attend_double_f16(qkv: np.ndarray, qn, kn, sinks, is_swa: bool, has_rope: bool, probe_pos=PROBE_POS,
+                      probe_heads=PROBE_HEADS) -> np.ndarray:
+    """The reference's all-double statement with half-rounded K/V (src/main.mm:253-305) at the probe positions and
+    heads: [n_pos][n_heads][128] float64."""
+    qkv = np.ascontiguousarray(qkv, np.float32)
+    pp, ph = np.asarray(probe_pos, np.int32), np.asarray(probe_heads, np.int32)
+    out = np.empty((len(pp), len(ph), HEAD_DIM), np.float64)
+    lib().fo_attend_double_f16(qkv.reshape(-1), qkv.shape[0], qn, kn, sinks, int(is_swa), int(has_rope), pp, len(pp), ph,
+                               len(ph), out.reshape(-1))
+    return out
+
+
+def grid_qkv(seed: int, n_tok: int) -> np.ndarray:
+    """Raw q|k|v rows [n_tok][5120] uniform on the grid {-2, -1.998, ..., 2}, the distribution of src/main.mm:247."""
+    out = np.empty(n_tok * QKV_DIM, np.float32)
+    lib().fo_gen_grid(seed, STREAM_QKV, 0, out.size, out)
+    return out.reshape(n_tok, QKV_DIM)
 
 
 def attend_partial(q, kc, vc, j0: int, j1: int) -> np.ndarray:

@@ -74,3 +74,28 @@ def test_f16cache_decode_matches_rounded_layer_forward(fo):
         for p in range(T):
             a = fo.decode_token_f16cache(qkv[p], p, qn, kn, sinks, is_swa, True, k16, v16)
             assert np.array_equal(a, att[p]), p
+
+
+@pytest.mark.parametrize("kind", ["full_nope", "swa_rope"])
+def test_second_cpu_statement_agrees_with_the_first(fo, kind):
+    """The reference states this path twice on the CPU: src/ref (fp32 scores, double accumulators, un-rounded cache)
+    and its attention unit test (src/main.mm:253-305: all double, K/V rounded through half).  On the unit test's own
+    workload -- 1300 tokens of grid-uniform rows, its probe positions and heads, a full/NoPE and a SWA/RoPE layer --
+    the restatements of both agree to fp32 rounding once the first one rounds K/V through half as well, and to the
+    size of that rounding when it does not."""
+    is_swa, has_rope = {"full_nope": (False, False), "swa_rope": (True, True)}[kind]
+    seed, T = 11, 1300
+    qn, kn, sinks = fo.layer_weights(seed, 0 if kind == "full_nope" else 2)
+    qkv = fo.grid_qkv(seed, T)
+    assert qkv.min() >= -2 and qkv.max() <= 2 and len(np.unique(qkv)) == 2001
+    second = fo.attend_double_f16(qkv, qn, kn, sinks, is_swa, has_rope)
+    pos, heads = list(fo.PROBE_POS), list(fo.PROBE_HEADS)
+    rounded, _, _ = fo.layer_forward(qkv, qn, kn, sinks, is_swa, has_rope, round_kv_f16=True, n_threads=8)
+    plain, _, _ = fo.layer_forward(qkv, qn, kn, sinks, is_swa, has_rope, round_kv_f16=False, n_threads=8)
+    rounded = rounded.reshape(T, 32, 128)[pos][:, heads]
+    plain = plain.reshape(T, 32, 128)[pos][:, heads]
+    # fp32 norm/RoPE can move a K element across a half rounding boundary: a handful of one-ulp differences in K
+    assert np.abs(rounded - second).max() < 1e-4
+    rms = np.sqrt((second ** 2).mean())
+    assert np.abs(plain - second).max() / rms < 2e-2  # the bar of the reference's test (src/main.mm:309)
+    assert np.abs(plain - second).max() < 2e-3
