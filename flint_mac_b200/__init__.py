@@ -4,3 +4,4 @@ The Python here is only a ctypes mirror of that ABI, in the role the reference's
 src/capi.h.  There is no CPU fallback: without the compiled library, or without a B200, calls fail loudly.
 """
 from .capi import Attn, FlintAttnError, load_library, F32, BF16, plan_decode, rollback_restart, decode_noalloc_dev, i32_array  # noqa: F401
+from .engine import Engine, write_model_file  # noqa: F401,E402

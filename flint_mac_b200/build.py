@@ -7,7 +7,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libflint_attn.so")
-SOURCES = ["flint_attn.cu", "decode_attn.cu", "prefill_attn.cu", "decode_noalloc.cu"]
+SOURCES = ["flint_attn.cu", "decode_attn.cu", "prefill_attn.cu", "decode_noalloc.cu", "proj.cu", "flint_shim.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-shared"]
 

@@ -56,6 +56,14 @@ SYMBOLS = {
                                        C.c_int32, C.c_char_p, C.c_int32]),
     "flint_attn_prefill_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p,
                                            C.c_int32, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_set_projections": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_decode_block_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_void_p,
+                                                C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_prefill_block_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                                 C.c_char_p, C.c_int32]),
+    "flint_attn_project_dev": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
     "flint_attn_check": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32]),
     "flint_attn_n_slots": (C.c_int32, [C.c_void_p, C.c_int32]),
     "flint_attn_read_kv": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
@@ -293,6 +301,28 @@ class Attn:
     def prefill_dev(self, layer, seq, n_tok, qkv_dev, qkv_dtype, out_dev, out_dtype, stream: int = 0):
         self._call("flint_attn_prefill_dev", layer, seq, n_tok, _ptr(qkv_dev), qkv_dtype, _ptr(out_dev), out_dtype,
                    stream)
+
+    # ---- the attention block with its projections (residual stream rows in, updated in place)
+    def set_projections(self, layer: int, attn_norm: np.ndarray, wq: np.ndarray, wk: np.ndarray, wv: np.ndarray,
+                        wo: np.ndarray):
+        """attn_norm fp32 [n_embd]; wq [4096][n_embd], wk/wv [512][n_embd], wo [n_embd][4096] as uint16 bf16 bits."""
+        attn_norm = np.ascontiguousarray(attn_norm, np.float32)
+        wq, wk, wv, wo = (np.ascontiguousarray(x, np.uint16) for x in (wq, wk, wv, wo))
+        n_embd = attn_norm.size
+        assert wq.shape == (4096, n_embd) and wk.shape == (512, n_embd) and wv.shape == (512, n_embd)
+        assert wo.shape == (n_embd, 4096)
+        self._call("flint_attn_set_projections", layer, n_embd, attn_norm.ctypes.data, wq.ctypes.data, wk.ctypes.data,
+                   wv.ctypes.data, wo.ctypes.data)
+
+    def decode_block_dev(self, layer, seqs, x_dev, stream: int = 0):
+        self._call("flint_attn_decode_block_dev", layer, len(seqs), _i32(seqs), _ptr(x_dev), stream)
+
+    def prefill_block_dev(self, layer, seq, n_tok, x_dev, stream: int = 0):
+        self._call("flint_attn_prefill_block_dev", layer, seq, n_tok, _ptr(x_dev), stream)
+
+    def project_dev(self, w_dev, n_rows_w, k, x_dev, n, norm_w_dev, out_dev, stream: int = 0):
+        self._call("flint_attn_project_dev", _ptr(w_dev), n_rows_w, k, _ptr(x_dev), n,
+                   _ptr(norm_w_dev) if norm_w_dev is not None else None, _ptr(out_dev), stream)
 
     def check(self):
         """Synchronise and raise if any asynchronous call of this handle failed on the device."""

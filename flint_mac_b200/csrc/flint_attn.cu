@@ -14,6 +14,7 @@
 #include "../../include/flint_attn.h"
 #include "attn_common.h"
 #include "prefill_attn.h"
+#include "proj.h"
 
 using namespace flint;
 
@@ -39,6 +40,11 @@ struct Layer {
     int kv_lo = 0, kv_hi = 0;  // positions a full layer holds on this device: [kv_lo, kv_hi)
     __half *k = nullptr, *v = nullptr;
     float *q_norm = nullptr, *k_norm = nullptr, *sinks = nullptr;  // device copies
+    // projections either side of attention (optional): attn_norm [n_embd] fp32, W_qkv [5120][n_embd] bf16 (q rows,
+    // then k rows, then v rows: the packed row of src/metal/fused.metal:211), W_o [n_embd][4096] bf16
+    int n_embd = 0;
+    float *attn_norm = nullptr;
+    __nv_bfloat16 *w_qkv = nullptr, *w_o = nullptr;
 };
 
 constexpr int kRing = 4;  // work lists in flight
@@ -192,6 +198,9 @@ struct flint_attn {
     void *io_dev = nullptr;         // device staging for host-buffer calls
     size_t io_cap = 0;
     PrefillWorkspace pf;
+    ProjWorkspace proj_ws;
+    float *block_buf = nullptr;  // [rows][5120 + 4096] fp32: the q|k|v rows and the attention rows of a block call
+    size_t block_rows = 0;
     int64_t launches = 0;
     std::vector<PlanCache> plan_cache;  // kPlanWays per layer
     std::vector<int> plan_victim;       // per layer: the way the next unknown batch replaces
@@ -216,7 +225,10 @@ struct flint_attn {
         cudaSetDevice(device);
         for (auto &L : layers) {
             cudaFree(L.k); cudaFree(L.v); cudaFree(L.q_norm); cudaFree(L.k_norm); cudaFree(L.sinks);
+            cudaFree(L.attn_norm); cudaFree(L.w_qkv); cudaFree(L.w_o);
         }
+        proj_workspace_free(proj_ws);
+        cudaFree(block_buf);
         cudaFree(inv_freq); cudaFree(scratch); cudaFree(scratch2); cudaFree(tickets); cudaFree(io_dev);
         for (int i = 0; i < kRing; i++) {
             if (ring_host[i]) cudaFreeHost(ring_host[i]);
@@ -756,6 +768,45 @@ static void prefill_impl(flint_attn *a, int layer, int seq, int n_tok, const voi
     a->launches += n_launch;
 }
 
+// The attention block of one layer as the reference engine runs it between two residual-stream states
+// (src/engine.mm:728-811 for one token, :1060-1112 for a prompt; src/ref/ref_model.cpp:108-151):
+//   qkv = W_qkv . rmsnorm(x, attn_norm);  att = attention(qkv);  x += W_o . att
+// The q|k|v rows and the attention rows stay in a scratch buffer of this handle (20 KB and 16 KB per token, which
+// live in L2 between the three launches); x is read and updated in place.
+static void attn_block(flint_attn *a, int layer, int n_rows, const int32_t *seqs, int seq, bool prefill, float *x,
+                       cudaStream_t st) {
+    CK(cudaSetDevice(a->device));
+    Layer &L = a->layer(layer);
+    if (!L.w_qkv) throw std::runtime_error("layer projections not set (flint_attn_set_projections)");
+    if (!x) throw std::runtime_error("null residual stream");
+    if (n_rows <= 0) throw std::runtime_error(prefill ? "empty prefill" : "batch size out of range");
+    if (size_t(n_rows) > a->block_rows) {
+        CK(cudaDeviceSynchronize());
+        cudaFree(a->block_buf);
+        a->block_buf = nullptr;
+        a->block_rows = 0;
+        const size_t rows = std::max<size_t>(size_t(n_rows), 64);
+        CK(cudaMalloc(&a->block_buf, rows * (kQkvDim + kQDim) * sizeof(float)));
+        a->block_rows = rows;
+    }
+    float *qkv = a->block_buf, *att = a->block_buf + a->block_rows * kQkvDim;
+    int n_launch = 0;
+    ProjCall pc{};
+    pc.w = L.w_qkv; pc.act = x; pc.act_dtype = kDtypeF32; pc.norm_w = L.attn_norm;
+    pc.out = qkv; pc.out_dtype = kDtypeF32; pc.residual = nullptr;
+    pc.B = n_rows; pc.N = kQkvDim; pc.K = L.n_embd;
+    CK(launch_proj(pc, a->proj_ws, a->sm_count, st, &n_launch));
+    a->launches += n_launch;
+    if (prefill) prefill_impl(a, layer, seq, n_rows, qkv, kDtypeF32, att, kDtypeF32, st);
+    else a->decode_dev(layer, n_rows, seqs, qkv, kDtypeF32, att, kDtypeF32, nullptr, 0, st);
+    pc = ProjCall{};
+    pc.w = L.w_o; pc.act = att; pc.act_dtype = kDtypeF32; pc.norm_w = nullptr;
+    pc.out = x; pc.out_dtype = kDtypeF32; pc.residual = x;
+    pc.B = n_rows; pc.N = L.n_embd; pc.K = kQDim;
+    CK(launch_proj(pc, a->proj_ws, a->sm_count, st, &n_launch));
+    a->launches += n_launch;
+}
+
 int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv_dev,
                                int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
                                int32_t err_len) {
@@ -784,6 +835,68 @@ int32_t flint_attn_prefill(flint_attn *a, int32_t layer, int32_t seq, int32_t n_
     int flag = 0;
     CK(prefill_error_flag(a->pf, &flag));
     if (flag) throw std::runtime_error("prefill kernel reported device error " + std::to_string(flag));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_set_projections(flint_attn *a, int32_t layer, int32_t n_embd, const float *attn_norm,
+                                   const uint16_t *wq, const uint16_t *wk, const uint16_t *wv, const uint16_t *wo,
+                                   char *err, int32_t err_len) {
+    API_TRY
+    if (layer < 0 || layer >= int(a->layers.size())) throw std::runtime_error("layer index out of range");
+    if (!attn_norm || !wq || !wk || !wv || !wo) throw std::runtime_error("null weight pointer");
+    if (n_embd <= 0 || n_embd % 256 != 0) throw std::runtime_error("n_embd must be a positive multiple of 256");
+    CK(cudaSetDevice(a->device));
+    Layer &L = a->layers[layer];
+    CK(cudaDeviceSynchronize());
+    cudaFree(L.attn_norm); cudaFree(L.w_qkv); cudaFree(L.w_o);
+    L.attn_norm = nullptr; L.w_qkv = nullptr; L.w_o = nullptr;
+    const size_t E = size_t(n_embd);
+    CK(cudaMalloc(&L.attn_norm, E * sizeof(float)));
+    CK(cudaMalloc(&L.w_qkv, size_t(kQkvDim) * E * 2));
+    CK(cudaMalloc(&L.w_o, E * kQDim * 2));
+    CK(cudaMemcpy(L.attn_norm, attn_norm, E * sizeof(float), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(L.w_qkv, wq, size_t(kQDim) * E * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(L.w_qkv + size_t(kQDim) * E, wk, size_t(kKvDim) * E * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(L.w_qkv + size_t(kQDim + kKvDim) * E, wv, size_t(kKvDim) * E * 2, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(L.w_o, wo, E * kQDim * 2, cudaMemcpyHostToDevice));
+    L.n_embd = n_embd;
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_decode_block_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs, float *x_dev,
+                                    void *cuda_stream, char *err, int32_t err_len) {
+    API_TRY
+    attn_block(a, layer, n, seqs, 0, false, x_dev, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_prefill_block_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, float *x_dev,
+                                     void *cuda_stream, char *err, int32_t err_len) {
+    API_TRY
+    attn_block(a, layer, n_tok, nullptr, seq, true, x_dev, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_project_dev(flint_attn *a, const uint16_t *w_dev, int32_t n_rows_w, int32_t k, const float *x_dev,
+                               int32_t n, const float *norm_w_dev, float *out_dev, void *cuda_stream, char *err,
+                               int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    if (!w_dev || !x_dev || !out_dev) throw std::runtime_error("null pointer");
+    if (n <= 0 || n_rows_w <= 0 || n_rows_w % kProjRowBlock != 0 || k <= 0 || k % 256 != 0)
+        throw std::runtime_error("projection shape: rows a multiple of 128, k a multiple of 256");
+    ProjCall pc{};
+    pc.w = reinterpret_cast<const __nv_bfloat16 *>(w_dev);
+    pc.act = x_dev; pc.act_dtype = kDtypeF32; pc.norm_w = norm_w_dev;
+    pc.out = out_dev; pc.out_dtype = kDtypeF32; pc.residual = nullptr;
+    pc.B = n; pc.N = n_rows_w; pc.K = k;
+    int n_launch = 0;
+    CK(launch_proj(pc, a->proj_ws, a->sm_count, cudaStream_t(cuda_stream), &n_launch));
+    a->launches += n_launch;
     return 0;
     API_CATCH(-1)
 }

@@ -140,6 +140,32 @@ int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_
                                int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
                                int32_t err_len);
 
+/* ---- the attention block with its projections ---------------------------------------------------------
+ * The steps either side of attention in the reference engine: the q/k/v matvecs on the attn_norm-ed residual stream
+ * (src/engine.mm:728-732; fused form k_qkv, src/metal/fused.metal:215-231) and the o-proj matvec with the residual
+ * add (src/engine.mm:811; k_mv_res, src/metal/fused.metal:357-379).  The reference's weights are quantised; here
+ * they are dense bf16 rows with the input dimension contiguous (the GGUF layout).  set_projections copies host
+ * arrays: attn_norm fp32 [n_embd], wq [4096][n_embd], wk [512][n_embd], wv [512][n_embd], wo [n_embd][4096] as bf16
+ * bits; n_embd a multiple of 256.
+ *   decode_block : x_dev fp32 [n][n_embd], one new token for each of n sequences, updated in place:
+ *                  x += W_o . attention(W_qkv . rmsnorm(x, attn_norm))     (src/ref/ref_model.cpp:108-151)
+ *   prefill_block: the same for n_tok tokens of one sequence from its current position.
+ * The q|k|v rows and the attention rows never leave the device (scratch of the handle).  Like the attention calls,
+ * these read the position and do not move it (flint_attn_advance after all layers). */
+int32_t flint_attn_set_projections(flint_attn *a, int32_t layer, int32_t n_embd, const float *attn_norm,
+                                   const uint16_t *wq, const uint16_t *wk, const uint16_t *wv, const uint16_t *wo,
+                                   char *err, int32_t err_len);
+int32_t flint_attn_decode_block_dev(flint_attn *a, int32_t layer, int32_t n, const int32_t *seqs, float *x_dev,
+                                    void *cuda_stream, char *err, int32_t err_len);
+int32_t flint_attn_prefill_block_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, float *x_dev,
+                                     void *cuda_stream, char *err, int32_t err_len);
+/* The projection kernel by itself (the reference's matvec, src/ref/ref_model.cpp:74-92, with an optional RMSNorm of
+ * the input rows folded in): out_dev fp32 [n][n_rows_w] = W . norm?(x), W = w_dev bf16 [n_rows_w][k] on the device,
+ * x_dev fp32 [n][k], norm_w_dev fp32 [k] or NULL.  n_rows_w a multiple of 128, k a multiple of 256. */
+int32_t flint_attn_project_dev(flint_attn *a, const uint16_t *w_dev, int32_t n_rows_w, int32_t k, const float *x_dev,
+                               int32_t n, const float *norm_w_dev, float *out_dev, void *cuda_stream, char *err,
+                               int32_t err_len);
+
 /* Wait for everything this handle enqueued and report an asynchronous failure of the *_dev calls (a CUDA error,
  * or a kernel whose bounded wait ran out), in the way the reference turns cb.error into an exception after
  * waitUntilCompleted (src/engine.mm:930-932).  A device-side error is reported by one call and cleared. */

@@ -338,6 +338,61 @@ void fo_gen_grid(uint64_t seed, uint64_t stream, uint64_t first, uint64_t n, flo
     for (uint64_t i = 0; i < n; i++) out[i] = ((int)(fo_gen_u64(seed, stream, first + i) % 2001) - 1000) / 500.0f;
 }
 
+/* ---- src/ref/ref_model.cpp:74-92, :95-197 with a zero feed-forward part ------------------------------------- */
+void fo_matvec(const float *w, const float *x, float *y, int n_rows, int k, int n_threads) {
+    if (n_threads < 1) n_threads = 1;
+#pragma omp parallel for num_threads(n_threads) if (n_threads > 1 && n_rows >= 256) schedule(static)
+    for (int r = 0; r < n_rows; r++) {
+        const float *row = w + (size_t)r * k;
+        double acc = 0;
+        for (int i = 0; i < k; i++) acc += (double)row[i] * x[i];
+        y[r] = (float)acc;
+    }
+}
+
+void fo_stack_forward(const float *embd, const float *attn_norm, const float *wq, const float *wk, const float *wv,
+                      const float *q_norm, const float *k_norm, const float *sinks, const float *wo,
+                      const int32_t *is_swa, const int32_t *has_rope, const float *out_norm, const float *w_out,
+                      const int32_t *tokens, int n_tok, int n_layer, int n_embd, int n_vocab, float *logits,
+                      float *hidden, int n_threads) {
+    const int E = n_embd;
+    float *x = (float *)malloc(sizeof(float) * E), *xn = (float *)malloc(sizeof(float) * E);
+    float *o = (float *)malloc(sizeof(float) * E);
+    float row[FO_QKV_DIM], att[FO_Q_DIM];
+    float **kc = (float **)malloc(sizeof(float *) * n_layer), **vc = (float **)malloc(sizeof(float *) * n_layer);
+    for (int il = 0; il < n_layer; il++) {
+        kc[il] = (float *)malloc(sizeof(float) * (size_t)n_tok * FO_KV_DIM);
+        vc[il] = (float *)malloc(sizeof(float) * (size_t)n_tok * FO_KV_DIM);
+    }
+    for (int t = 0; t < n_tok; t++) {
+        const int pos = t;
+        memcpy(x, embd + (size_t)tokens[t] * E, sizeof(float) * E); /* ref_model.cpp:102 */
+        for (int il = 0; il < n_layer; il++) {
+            fo_rmsnorm(x, attn_norm + (size_t)il * E, xn, E, FO_RMS_EPS); /* :108 */
+            fo_matvec(wq + (size_t)il * FO_Q_DIM * E, xn, row, FO_Q_DIM, E, n_threads); /* :109-111 */
+            fo_matvec(wk + (size_t)il * FO_KV_DIM * E, xn, row + FO_Q_DIM, FO_KV_DIM, E, n_threads);
+            fo_matvec(wv + (size_t)il * FO_KV_DIM * E, xn, row + FO_Q_DIM + FO_KV_DIM, FO_KV_DIM, E, n_threads);
+            fo_qk_norm_rope(row, q_norm + il * FO_HEAD_DIM, k_norm + il * FO_HEAD_DIM, pos, has_rope[il]); /* :112-121 */
+            memcpy(kc[il] + (size_t)pos * FO_KV_DIM, row + FO_Q_DIM, sizeof(float) * FO_KV_DIM); /* :122-124 */
+            memcpy(vc[il] + (size_t)pos * FO_KV_DIM, row + FO_Q_DIM + FO_KV_DIM, sizeof(float) * FO_KV_DIM);
+            fo_attend(row, kc[il], vc[il], sinks + il * FO_N_HEAD, pos, is_swa[il], att, n_threads); /* :125-149 */
+            fo_matvec(wo + (size_t)il * E * FO_Q_DIM, att, o, E, FO_Q_DIM, n_threads); /* :150 */
+            for (int i = 0; i < E; i++) x[i] += o[i]; /* :151 */
+            /* the feed-forward half (:153-188) adds zero */
+        }
+        if (hidden) memcpy(hidden + (size_t)t * E, x, sizeof(float) * E);
+        if (logits) {
+            fo_rmsnorm(x, out_norm, xn, E, FO_RMS_EPS); /* :192 */
+            fo_matvec(w_out, xn, logits + (size_t)t * n_vocab, n_vocab, E, n_threads); /* :194 */
+        }
+    }
+    for (int il = 0; il < n_layer; il++) {
+        free(kc[il]);
+        free(vc[il]);
+    }
+    free(kc); free(vc); free(x); free(xn); free(o);
+}
+
 int32_t fo_slot(int32_t pos, int is_swa) { return is_swa ? (pos & (FO_SWA_RING - 1)) : pos; }
 
 int32_t fo_k_begin(int32_t pos, int is_swa) {

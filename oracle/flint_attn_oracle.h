@@ -111,6 +111,23 @@ void fo_attend_double_f16(const float *qkv, int n, const float *q_norm, const fl
  * {-2, -1.998, ..., 2}, here from the seeded generator (rand() itself is platform-specific). */
 void fo_gen_grid(uint64_t seed, uint64_t stream, uint64_t first, uint64_t n, float *out);
 
+/* ---- the attention stack of the whole model (projections, residual, logits) ----------------------------------
+ * src/ref/ref_model.cpp:74-92: y[r] = float(sum_i double(w[r][i]) * x[i]), rows r of w [n_rows][k]. */
+void fo_matvec(const float *w, const float *x, float *y, int n_rows, int k, int n_threads);
+/* RefModel::forward (src/ref/ref_model.cpp:95-197) for a model whose feed-forward weights are zero, token by token
+ * from position 0: embedding row, per layer rmsnorm -> q/k/v matvecs -> QK norm (+RoPE) -> attention over the
+ * un-rounded fp32 cache -> o-proj matvec -> residual add; then output_norm and the vocabulary matvec.  All weights
+ * as fp32 arrays (whatever precision they were rounded to beforehand):
+ *   embd [n_vocab][E]; per layer l: attn_norm [L][E], wq [L][4096][E], wk [L][512][E], wv [L][512][E],
+ *   q_norm [L][128], k_norm [L][128], sinks [L][32], wo [L][E][4096]; out_norm [E]; w_out [n_vocab][E].
+ * logits [n_tok][n_vocab] and hidden [n_tok][E] (the residual stream after the last layer) are written for every
+ * token; either may be NULL. */
+void fo_stack_forward(const float *embd, const float *attn_norm, const float *wq, const float *wk, const float *wv,
+                      const float *q_norm, const float *k_norm, const float *sinks, const float *wo,
+                      const int32_t *is_swa, const int32_t *has_rope, const float *out_norm, const float *w_out,
+                      const int32_t *tokens, int n_tok, int n_layer, int n_embd, int n_vocab, float *logits,
+                      float *hidden, int n_threads);
+
 /* ---- integer maps (bit-exact items) ------------------------------------------ */
 /* src/metal/fused.metal:269-274, prefill.metal:106 */
 int32_t fo_slot(int32_t pos, int is_swa);

@@ -65,6 +65,9 @@ def lib():
         L.fo_attend_double_f16.argtypes = [_f32p, C.c_int, _f32p, _f32p, _f32p, C.c_int, C.c_int, _i32p, C.c_int, _i32p,
                                            C.c_int, np.ctypeslib.ndpointer(np.float64, flags="C_CONTIGUOUS")]
         L.fo_gen_grid.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, _f32p]
+        L.fo_matvec.argtypes = [_f32p, _f32p, _f32p, C.c_int, C.c_int, C.c_int]
+        L.fo_stack_forward.argtypes = [_f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _f32p, _i32p, _i32p, _f32p,
+                                       _f32p, _i32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
         L.fo_slot.argtypes = [C.c_int32, C.c_int]
         L.fo_slot.restype = C.c_int32
         L.fo_k_begin.argtypes = [C.c_int32, C.c_int]
@@ -227,6 +230,59 @@ def combine(part: np.ndarray, sinks) -> np.ndarray:
     out = np.empty((N_HEAD, HEAD_DIM), np.float32)
     lib().fo_combine(part.reshape(-1), part.shape[1], sinks, out.reshape(-1))
     return out
+
+
+# ---------------------------------------------------------------- the attention stack with its projections
+STREAM_EMBD, STREAM_ATTN_NORM, STREAM_WQ, STREAM_WK, STREAM_WV, STREAM_WO, STREAM_OUT_NORM, STREAM_WOUT = range(8, 16)
+
+
+def matvec(w: np.ndarray, x: np.ndarray, n_threads: int = 1) -> np.ndarray:
+    """y = W x with a double accumulator per row (src/ref/ref_model.cpp:74-92)."""
+    w = np.ascontiguousarray(w, np.float32)
+    y = np.empty(w.shape[0], np.float32)
+    lib().fo_matvec(w.reshape(-1), np.ascontiguousarray(x, np.float32), y, w.shape[0], w.shape[1], n_threads)
+    return y
+
+
+def stack_weights(seed: int, n_layer: int, n_embd: int, n_vocab: int, layer_kinds):
+    """Seeded weights of a small attention stack, every matrix rounded to bf16 (what the GPU holds): projections
+    ~ N(0, 0.02), norms ~ 1 + N(0, 0.1), sinks ~ N(0, 1), embeddings ~ N(0, 1).  layer_kinds: [(is_swa, has_rope)].
+    Returns a dict of fp32 arrays."""
+    E = n_embd
+    w = {"n_layer": n_layer, "n_embd": E, "n_vocab": n_vocab,
+         "is_swa": np.array([int(k[0]) for k in layer_kinds], np.int32),
+         "has_rope": np.array([int(k[1]) for k in layer_kinds], np.int32),
+         "embd": round_bf16(gen_normal(seed, STREAM_EMBD, n_vocab * E)).reshape(n_vocab, E),
+         "out_norm": gen_normal(seed, STREAM_OUT_NORM, E, 1.0, 0.1),
+         "w_out": round_bf16(gen_normal(seed, STREAM_WOUT, n_vocab * E, 0.0, 0.02)).reshape(n_vocab, E)}
+    per = {"attn_norm": [], "wq": [], "wk": [], "wv": [], "wo": [], "q_norm": [], "k_norm": [], "sinks": []}
+    for il in range(n_layer):
+        per["attn_norm"].append(gen_normal(seed, STREAM_ATTN_NORM + 16 * il, E, 1.0, 0.1))
+        per["wq"].append(round_bf16(gen_normal(seed, STREAM_WQ + 16 * il, Q_DIM * E, 0.0, 0.02)).reshape(Q_DIM, E))
+        per["wk"].append(round_bf16(gen_normal(seed, STREAM_WK + 16 * il, KV_DIM * E, 0.0, 0.02)).reshape(KV_DIM, E))
+        per["wv"].append(round_bf16(gen_normal(seed, STREAM_WV + 16 * il, KV_DIM * E, 0.0, 0.02)).reshape(KV_DIM, E))
+        per["wo"].append(round_bf16(gen_normal(seed, STREAM_WO + 16 * il, E * Q_DIM, 0.0, 0.02)).reshape(E, Q_DIM))
+        qn, kn, sk = layer_weights(seed, il)
+        per["q_norm"].append(qn); per["k_norm"].append(kn); per["sinks"].append(sk)
+    for k, v in per.items():
+        w[k] = np.ascontiguousarray(np.stack(v), np.float32)
+    return w
+
+
+def stack_forward(w: dict, tokens, want_logits: bool = True, want_hidden: bool = True, n_threads: int = 8):
+    """The reference's forward pass with a zero feed-forward half (src/ref/ref_model.cpp:95-197), token by token from
+    position 0.  Returns (logits [n_tok][n_vocab] or None, hidden [n_tok][n_embd] or None)."""
+    tokens = np.ascontiguousarray(tokens, np.int32)
+    n = tokens.size
+    logits = np.empty((n, w["n_vocab"]), np.float32) if want_logits else None
+    hidden = np.empty((n, w["n_embd"]), np.float32) if want_hidden else None
+    f = lambda a: np.ascontiguousarray(a, np.float32).reshape(-1)  # noqa: E731
+    lib().fo_stack_forward(f(w["embd"]), f(w["attn_norm"]), f(w["wq"]), f(w["wk"]), f(w["wv"]), f(w["q_norm"]),
+                           f(w["k_norm"]), f(w["sinks"]), f(w["wo"]), w["is_swa"], w["has_rope"], f(w["out_norm"]),
+                           f(w["w_out"]), tokens, n, w["n_layer"], w["n_embd"], w["n_vocab"],
+                           logits.ctypes.data if want_logits else None, hidden.ctypes.data if want_hidden else None,
+                           n_threads)
+    return logits, hidden
 
 
 # ---------------------------------------------------------------- integer maps

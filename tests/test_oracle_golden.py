@@ -99,3 +99,17 @@ def test_second_cpu_statement_agrees_with_the_first(fo, kind):
     rms = np.sqrt((second ** 2).mean())
     assert np.abs(plain - second).max() / rms < 2e-2  # the bar of the reference's test (src/main.mm:309)
     assert np.abs(plain - second).max() < 2e-3
+
+
+def test_stack_restatement_matches_reference_refmodel(fo):
+    """The attention stack with real projections (rmsnorm -> q/k/v matvecs -> attention -> o-proj -> residual, then
+    output norm and vocabulary matvec): the restatement reproduces, bit for bit, the logits and residual stream the
+    unmodified RefModel produced on the same weights and tokens (tests/golden/make_golden_stack.py)."""
+    g = np.load(os.path.join(GOLD, "ref_stack.npz"))
+    kinds = list(zip(g["is_swa"].tolist(), g["has_rope"].tolist()))
+    w = fo.stack_weights(int(g["seed"]), int(g["n_layer"]), int(g["n_embd"]), int(g["n_vocab"]), kinds)
+    logits, hidden = fo.stack_forward(w, g["tokens"])
+    assert np.array_equal(logits[g["probe_pos"]], g["probe_logits"])
+    assert np.array_equal(logits.argmax(1), g["argmax"])
+    assert np.array_equal(logits.astype(np.float64).sum(1), g["logit_sum"])
+    assert np.array_equal(hidden.astype(np.float64).sum(1), g["hidden_sum"])
