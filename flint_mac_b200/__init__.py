@@ -5,3 +5,4 @@ src/capi.h.  There is no CPU fallback: without the compiled library, or without 
 """
 from .capi import Attn, FlintAttnError, load_library, F32, BF16, plan_decode, rollback_restart, decode_noalloc_dev, i32_array  # noqa: F401
 from .engine import Engine, write_model_file  # noqa: F401,E402
+from .sched import ContinuousBatcher, Router  # noqa: F401,E402

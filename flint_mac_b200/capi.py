@@ -24,7 +24,7 @@ class FlintAttnError(RuntimeError):
 class _Config(C.Structure):
     _fields_ = [("device", C.c_int32), ("n_layers", C.c_int32), ("layer_is_swa", C.POINTER(C.c_int32)),
                 ("layer_has_rope", C.POINTER(C.c_int32)), ("max_seqs", C.c_int32), ("n_ctx", C.c_int32),
-                ("kv_rank", C.c_int32), ("kv_ranks", C.c_int32)]
+                ("kv_rank", C.c_int32), ("kv_ranks", C.c_int32), ("kv_pages", C.c_int32)]
 
 
 SYMBOLS = {
@@ -72,6 +72,8 @@ SYMBOLS = {
                                         C.c_char_p, C.c_int32]),
     "flint_attn_kv_dev": (C.c_void_p, [C.c_void_p, C.c_int32, C.c_int32]),
     "flint_attn_set_pos": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32]),
+    "flint_attn_seq_release": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "flint_attn_pages_free": (C.c_int32, [C.c_void_p]),
     "flint_attn_plan_decode": (C.c_int32, [C.c_int32, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                            C.POINTER(C.c_int32), C.c_int32]),
     "flint_attn_set_target_items": (C.c_int32, [C.c_void_p, C.c_int32]),
@@ -160,12 +162,12 @@ class Attn:
     """One attention handle on one GPU. Single owner, not thread-safe (src/capi.h:1)."""
 
     def __init__(self, layer_is_swa: Sequence[bool], layer_has_rope: Sequence[bool], max_seqs: int, n_ctx: int,
-                 device: int = 0, kv_rank: int = 0, kv_ranks: int = 1):
+                 device: int = 0, kv_rank: int = 0, kv_ranks: int = 1, kv_pages: int = 0):
         self._lib = load_library()
         self._err = C.create_string_buffer(ERR_LEN)
         self.n_layers = len(layer_is_swa)
         swa, rope = _i32([int(b) for b in layer_is_swa]), _i32([int(b) for b in layer_has_rope])
-        cfg = _Config(device, self.n_layers, swa, rope, max_seqs, n_ctx, kv_rank, kv_ranks)
+        cfg = _Config(device, self.n_layers, swa, rope, max_seqs, n_ctx, kv_rank, kv_ranks, kv_pages)
         err = C.create_string_buffer(ERR_LEN)
         self._h = self._lib.flint_attn_open(C.byref(cfg), err, ERR_LEN)
         if not self._h:
@@ -205,6 +207,13 @@ class Attn:
 
     def advance(self, seqs: Sequence[int], n_tokens: int = 1) -> int:
         return int(self._lib.flint_attn_advance(self._h, len(seqs), _i32(seqs), n_tokens))
+
+    def seq_release(self, seq: int) -> int:
+        """Retire a sequence slot: position 0, its KV pages back to the pool."""
+        return int(self._lib.flint_attn_seq_release(self._h, seq))
+
+    def pages_free(self) -> int:
+        return int(self._lib.flint_attn_pages_free(self._h))
 
     def set_layer(self, layer: int, q_norm: np.ndarray, k_norm: np.ndarray, sinks: np.ndarray):
         q_norm, k_norm, sinks = (np.ascontiguousarray(x, np.float32) for x in (q_norm, k_norm, sinks))

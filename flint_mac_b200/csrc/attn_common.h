@@ -71,7 +71,14 @@ struct DecParams {
     uint32_t step;
     int *groups_done;       // one counter, zero between launches
     int n_groups;
+    // Paged full-attention layers: k_cache / v_cache are page pools [n_pages][4][64][128] and the 64-key block b of
+    // sequence s lives in page block_table[s * table_stride + b].  Work items then start on multiples of 64 keys, so a
+    // 64-key tile is exactly one page.
+    const int32_t *block_table;
+    int table_stride;
+    int paged;
 };
+constexpr int kPageKeys = 64;                   // keys per KV page = one decode tile
 
 struct CombineParams {
     const float *partials;  // [n_parts][n][32][130]

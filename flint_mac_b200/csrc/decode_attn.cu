@@ -208,17 +208,25 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     auto load_tile = [&](int t) {
         const int stage = t % kStages;
         const int jt = j0 + t * kTileKeys;
+        // paged layer: this tile is one page (jt is a multiple of 64); its rows are slots 0..63 of the page
+        const __half *kb = kbase, *vb = vbase;
+        if (p.paged) {
+            const size_t page = size_t(p.block_table[size_t(it.seq) * p.table_stride + (jt >> 6)]);
+            const size_t off = (page * kNHeadKv + it.kvh) * kPageKeys * kHeadDim;
+            kb = p.k_cache + off;
+            vb = p.v_cache + off;
+        }
 #pragma unroll
         for (int i = 0; i < (kTileKeys * 16) / kThreads; i++) {
             const int c = tid + kThreads * i;
             const int row = c >> 4, ch = c & 15;
             const int j = jt + row;
             const bool valid = j < j1;  // cached keys only; other rows are zero-filled
-            const int slot = valid ? int(uint32_t(j) & p.slot_mask) - p.kv_lo : 0;
+            const int slot = !valid ? 0 : p.paged ? row : int(uint32_t(j) & p.slot_mask) - p.kv_lo;
             const size_t off = size_t(slot) * kHeadDim + ch * 8;
             const uint32_t dst = stage * kTileBytes + row * kRowBytes + ((ch ^ (row & 7)) << 4);
-            cp_async16(ks_addr + dst, kbase + off, valid ? 16u : 0u);
-            cp_async16(vs_addr + dst, vbase + off, valid ? 16u : 0u);
+            cp_async16(ks_addr + dst, kb + off, valid ? 16u : 0u);
+            cp_async16(vs_addr + dst, vb + off, valid ? 16u : 0u);
         }
     };
 
@@ -277,8 +285,14 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         if (fold_k || fold_v) {
             if (fold_k) kv_new = norm_rope(kv_new, wk, cs, sn, lane, rope);
             store_half4(fold_k ? &sm.knew[4 * lane] : &sm.vnew[4 * lane], kv_new);
-            const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
-            store_half4(const_cast<__half *>(fold_k ? kbase : vbase) + size_t(slot) * kHeadDim + 4 * lane, kv_new);
+            if (p.paged) {
+                const size_t page = size_t(p.block_table[size_t(it.seq) * p.table_stride + (it.pos >> 6)]);
+                const size_t off = ((page * kNHeadKv + it.kvh) * kPageKeys + (it.pos & (kPageKeys - 1))) * kHeadDim;
+                store_half4((fold_k ? p.k_cache : p.v_cache) + off + 4 * lane, kv_new);
+            } else {
+                const int slot = int(uint32_t(it.pos) & p.slot_mask) - p.kv_lo;
+                store_half4(const_cast<__half *>(fold_k ? kbase : vbase) + size_t(slot) * kHeadDim + 4 * lane, kv_new);
+            }
         }
     }
     __syncthreads();

@@ -36,6 +36,7 @@ void set_err(char *err, int32_t len, const char *msg) {  // src/capi.mm:17-22
 
 struct Layer {
     bool is_swa = false, has_rope = false, has_weights = false;
+    bool paged = false;  // full layer whose K/V live in a page pool [kv_pages][4][64][128] shared by all sequences
     int n_slots = 0;
     int kv_lo = 0, kv_hi = 0;  // positions a full layer holds on this device: [kv_lo, kv_hi)
     __half *k = nullptr, *v = nullptr;
@@ -181,6 +182,13 @@ bool patch_plan(PlanCache &pc, int n, const int32_t *seqs, const int32_t *pos, b
 struct flint_attn {
     int device = 0, max_seqs = 0, n_ctx = 0, kv_rank = 0, kv_ranks = 1;
     int sm_count = 148, target_items = 0;
+    // Paged KV (kv_pages > 0): one block table and one free list serve every paged layer -- all full layers hold the
+    // same positions of a sequence, so block b of sequence s is page table[s][b] in each layer's own pool.
+    int kv_pages = 0, pages_per_seq = 0;
+    std::vector<int32_t> table_host;   // [max_seqs][pages_per_seq], -1 = no page
+    std::vector<int32_t> seq_blocks;   // blocks each sequence holds
+    std::vector<int32_t> free_pages;   // stack of free page numbers
+    int32_t *table_dev = nullptr;
     std::vector<Layer> layers;
     std::vector<int32_t> pos;
     float *inv_freq = nullptr;
@@ -229,6 +237,7 @@ struct flint_attn {
         }
         proj_workspace_free(proj_ws);
         cudaFree(block_buf);
+        cudaFree(table_dev);
         cudaFree(inv_freq); cudaFree(scratch); cudaFree(scratch2); cudaFree(tickets); cudaFree(io_dev);
         for (int i = 0; i < kRing; i++) {
             if (ring_host[i]) cudaFreeHost(ring_host[i]);
@@ -261,6 +270,24 @@ struct flint_attn {
         Layer &L = layers[il];
         if (!L.has_weights) throw std::runtime_error("layer weights not set (flint_attn_set_layer)");
         return L;
+    }
+
+    // Make sure sequence `seq` owns the pages of positions [0, last_pos].  New table entries are uploaded on `st`, in
+    // front of the launch that will read them (pageable source: staged before the call returns); entries that
+    // kernels already in flight read are never rewritten.
+    void ensure_pages(int seq, int last_pos, cudaStream_t st) {
+        const int need = last_pos / kPageKeys + 1, have = seq_blocks[seq];
+        if (need <= have) return;
+        if (size_t(need - have) > free_pages.size())
+            throw std::runtime_error("KV page pool exhausted (" + std::to_string(kv_pages) + " pages of 64 keys)");
+        int32_t *row = table_host.data() + size_t(seq) * pages_per_seq;
+        for (int b = have; b < need; b++) {
+            row[b] = free_pages.back();
+            free_pages.pop_back();
+        }
+        CK(cudaMemcpyAsync(table_dev + size_t(seq) * pages_per_seq + have, row + have, size_t(need - have) * sizeof(int32_t),
+                           cudaMemcpyHostToDevice, st));
+        seq_blocks[seq] = need;
     }
 
     void check_seqs(int n, const int32_t *seqs) const {
@@ -360,6 +387,13 @@ struct flint_attn {
             if (seen[seqs[i]] == batch_no) throw std::runtime_error("a sequence appears twice in one decode batch");
             seen[seqs[i]] = batch_no;
         }
+        if (L.paged) {  // all or nothing: a batch that does not fit the pool takes no page
+            size_t want = 0;
+            for (int i = 0; i < n; i++) want += size_t(std::max(0, p[i] / kPageKeys + 1 - seq_blocks[seqs[i]]));
+            if (want > free_pages.size())
+                throw std::runtime_error("KV page pool exhausted (" + std::to_string(kv_pages) + " pages of 64 keys)");
+            for (int i = 0; i < n; i++) ensure_pages(seqs[i], p[i], st);
+        }
         PlanCache *hit = nullptr;
         for (int w = 0; w < kPlanWays && !hit; w++) {
             PlanCache &c = plan_cache[size_t(il) * kPlanWays + w];
@@ -416,6 +450,9 @@ struct flint_attn {
         dp.has_rope = L.has_rope;
         dp.qkv_dtype = qkv_dtype; dp.out_dtype = out_dtype;
         dp.mode = mode;
+        dp.paged = L.paged ? 1 : 0;
+        dp.block_table = table_dev;
+        dp.table_stride = pages_per_seq;
         if (mode == 2) {
             const size_t rec_bytes = size_t(xchg_n) * kNHead * kPartialDim * sizeof(float);
             const size_t buf_off = 256 + size_t(step & 1) * kv_ranks * rec_bytes + size_t(kv_rank) * rec_bytes;
@@ -457,6 +494,8 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
         if (cfg->max_seqs <= 0 || cfg->n_ctx <= 0) throw std::runtime_error("max_seqs and n_ctx must be positive");
         const int ranks = cfg->kv_ranks > 1 ? cfg->kv_ranks : 1;
         if (cfg->kv_rank < 0 || cfg->kv_rank >= ranks) throw std::runtime_error("kv_rank out of range");
+        if (cfg->kv_pages < 0) throw std::runtime_error("kv_pages must not be negative");
+        if (cfg->kv_pages > 0 && ranks > 1) throw std::runtime_error("a paged KV cache cannot also be sharded by key range");
         int n_dev = 0;
         CK(cudaGetDeviceCount(&n_dev));
         if (cfg->device < 0 || cfg->device >= n_dev) throw std::runtime_error("no such CUDA device");
@@ -475,6 +514,16 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
         a->sm_count = prop.multiProcessorCount;
         a->target_items = a->sm_count * 2;
         a->pos.assign(cfg->max_seqs, 0);
+        if (cfg->kv_pages > 0) {
+            a->kv_pages = cfg->kv_pages;
+            a->pages_per_seq = (cfg->n_ctx + kPageKeys - 1) / kPageKeys;
+            a->table_host.assign(size_t(cfg->max_seqs) * a->pages_per_seq, -1);
+            a->seq_blocks.assign(cfg->max_seqs, 0);
+            a->free_pages.resize(cfg->kv_pages);
+            for (int i = 0; i < cfg->kv_pages; i++) a->free_pages[i] = cfg->kv_pages - 1 - i;  // page 0 is handed out first
+            CK(cudaMalloc(&a->table_dev, a->table_host.size() * sizeof(int32_t)));
+            CK(cudaMemset(a->table_dev, 0xff, a->table_host.size() * sizeof(int32_t)));
+        }
         CK(cudaStreamCreateWithFlags(&a->stream, cudaStreamNonBlocking));
         for (int i = 0; i < kRing; i++) CK(cudaEventCreateWithFlags(&a->ring_ev[i], cudaEventDisableTiming));
         CK(decode_kernel_setup());
@@ -500,7 +549,9 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
                 L.kv_hi = std::min(cfg->n_ctx, L.kv_lo + shard);
                 L.n_slots = std::max(1, L.kv_hi - L.kv_lo);
             }
-            const size_t bytes = size_t(cfg->max_seqs) * kNHeadKv * L.n_slots * kHeadDim * sizeof(__half);
+            L.paged = !L.is_swa && cfg->kv_pages > 0;
+            const size_t bytes = L.paged ? size_t(cfg->kv_pages) * kNHeadKv * kPageKeys * kHeadDim * sizeof(__half)
+                                         : size_t(cfg->max_seqs) * kNHeadKv * L.n_slots * kHeadDim * sizeof(__half);
             CK(cudaMalloc(&L.k, bytes));
             CK(cudaMalloc(&L.v, bytes));
             CK(cudaMemset(L.k, 0, bytes));
@@ -754,8 +805,14 @@ static void prefill_impl(flint_attn *a, int layer, int seq, int n_tok, const voi
     pp.qkv = qkv; pp.out = out;
     pp.qkv_dtype = qkv_dtype; pp.out_dtype = out_dtype;
     pp.q_norm = L.q_norm; pp.k_norm = L.k_norm; pp.sinks = L.sinks; pp.inv_freq = a->inv_freq;
-    pp.k_cache = L.k + size_t(seq) * kNHeadKv * L.n_slots * kHeadDim;
-    pp.v_cache = L.v + size_t(seq) * kNHeadKv * L.n_slots * kHeadDim;
+    pp.k_cache = L.k + (L.paged ? 0 : size_t(seq) * kNHeadKv * L.n_slots * kHeadDim);
+    pp.v_cache = L.v + (L.paged ? 0 : size_t(seq) * kNHeadKv * L.n_slots * kHeadDim);
+    if (L.paged) {
+        a->ensure_pages(seq, p0 + n_tok - 1, st);
+        pp.block_table = a->table_dev + size_t(seq) * a->pages_per_seq;
+        pp.n_pages = a->kv_pages;
+        pp.table_len = a->pages_per_seq;
+    }
     pp.n_slots = L.n_slots;
     pp.is_swa = L.is_swa; pp.has_rope = L.has_rope;
     pp.p0 = p0; pp.n_tok = n_tok;
@@ -934,6 +991,34 @@ static void kv_copy(flint_attn *a, int layer, int seq, int slot0, int n, uint16_
     if (seq < 0 || seq >= a->max_seqs) throw std::runtime_error("sequence index out of range");
     if (slot0 < 0 || n < 0 || slot0 + n > L.n_slots) throw std::runtime_error("slot range out of bounds");
     CK(cudaDeviceSynchronize());
+    if (L.paged) {  // block by block through the table; writing allocates the pages it needs
+        if (!to_host && n > 0) {
+            a->ensure_pages(seq, slot0 + n - 1, nullptr);
+            CK(cudaDeviceSynchronize());
+        }
+        for (int s = slot0; s < slot0 + n;) {
+            const int b = s / kPageKeys, in_page = s % kPageKeys, cnt = std::min(kPageKeys - in_page, slot0 + n - s);
+            const int page = b < a->seq_blocks[seq] ? a->table_host[size_t(seq) * a->pages_per_seq + b] : -1;
+            for (int kvh = 0; kvh < kNHeadKv; kvh++) {
+                const size_t hoff = (size_t(kvh) * n + (s - slot0)) * kHeadDim, bytes = size_t(cnt) * kHeadDim * 2;
+                if (page < 0) {  // reading slots that were never written: zeros, as in a fresh contiguous cache
+                    memset(k + hoff, 0, bytes);
+                    memset(v + hoff, 0, bytes);
+                    continue;
+                }
+                const size_t doff = ((size_t(page) * kNHeadKv + kvh) * kPageKeys + in_page) * kHeadDim;
+                if (to_host) {
+                    CK(cudaMemcpy(k + hoff, L.k + doff, bytes, cudaMemcpyDeviceToHost));
+                    CK(cudaMemcpy(v + hoff, L.v + doff, bytes, cudaMemcpyDeviceToHost));
+                } else {
+                    CK(cudaMemcpy(L.k + doff, k + hoff, bytes, cudaMemcpyHostToDevice));
+                    CK(cudaMemcpy(L.v + doff, v + hoff, bytes, cudaMemcpyHostToDevice));
+                }
+            }
+            s += cnt;
+        }
+        return;
+    }
     for (int kvh = 0; kvh < kNHeadKv; kvh++) {
         const size_t doff = ((size_t(seq) * kNHeadKv + kvh) * L.n_slots + slot0) * kHeadDim;
         const size_t hoff = size_t(kvh) * n * kHeadDim, bytes = size_t(n) * kHeadDim * 2;
@@ -967,6 +1052,22 @@ void *flint_attn_kv_dev(flint_attn *a, int32_t layer, int32_t which) {
     if (layer < 0 || layer >= int(a->layers.size())) return nullptr;
     return which == 0 ? static_cast<void *>(a->layers[layer].k) : static_cast<void *>(a->layers[layer].v);
 }
+
+int32_t flint_attn_seq_release(flint_attn *a, int32_t seq) {
+    if (seq < 0 || seq >= a->max_seqs) return -1;
+    a->pos[seq] = 0;
+    if (a->kv_pages > 0) {
+        int32_t *row = a->table_host.data() + size_t(seq) * a->pages_per_seq;
+        for (int b = a->seq_blocks[seq] - 1; b >= 0; b--) {
+            a->free_pages.push_back(row[b]);
+            row[b] = -1;
+        }
+        a->seq_blocks[seq] = 0;
+    }
+    return 0;
+}
+
+int32_t flint_attn_pages_free(const flint_attn *a) { return a->kv_pages > 0 ? int32_t(a->free_pages.size()) : -1; }
 
 int32_t flint_attn_plan_decode(int32_t n, const int32_t *pos, int32_t is_swa, int32_t kv_lo, int32_t kv_hi,
                                int32_t target_items, int32_t *out, int32_t cap) {

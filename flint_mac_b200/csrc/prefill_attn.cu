@@ -77,6 +77,10 @@ struct PfArgs {
     // tiles; each range writes an un-normalised fp32 partial (rows s * t_pad + t of `out`) and its (m, l) per row.
     int n_ksplit, t_pad;
     float2 *part_ml;  // [n_ksplit * t_pad][32] (m in base-2 units, l)
+    // paged full layer: the K/V maps cover the page pool {128 dims, 64 rows, n_pages * 4} and the 64-key block b of
+    // the sequence is page block_table[b] (entries past the sequence's last page are negative)
+    const int32_t *block_table;
+    int table_len;
 };
 
 // ------------------------------------------------------------------------------------------------- prologue
@@ -89,6 +93,7 @@ struct PrologueArgs {
     int n_slots, is_swa, has_rope, qkv_dtype;
     int p0, n_tok, n_hist;
     int history_pass;  // 1: only copy the history rows out of the ring; 0: only the new tokens
+    const int32_t *block_table;  // paged full layer: k_cache / v_cache are page pools, slot = page * 64 + pos % 64
 };
 
 __device__ __forceinline__ float4 pf_load_row4(const void *base, int dtype, size_t elem0, int lane) {
@@ -168,6 +173,8 @@ __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) 
     }
     const float4 wk = reinterpret_cast<const float4 *>(a.k_norm)[lane];
     const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos;  // prefill.metal:106
+    // paged layer: [page][kv head][64 slots][128] instead of [kv head][slot][128]
+    const size_t page = a.block_table ? size_t(a.block_table[pos >> 6]) : 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
         const bool is_k = i < kNHeadKv;
@@ -177,7 +184,8 @@ __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) 
         // stores there, so the ring's final contents do not depend on the order in which the CTAs run.
         if (!a.is_swa || t + kSwaRing >= a.n_tok) {
             __half *cache = is_k ? a.k_cache : a.v_cache;
-            pf_store_half4(cache + (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane, y);
+            const size_t row = a.block_table ? (page * kNHeadKv + kvh) * 64 + (pos & 63) : size_t(kvh) * a.n_slots + slot;
+            pf_store_half4(cache + row * kHeadDim + 4 * lane, y);
         }
         if (a.k_st) {
             __half *st = is_k ? a.k_st : a.v_st;
@@ -336,6 +344,19 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 const uint32_t dst = base + kOffKV + slot * kTileBytes, full = bar(kBarSlotFull + slot);
                 const int row = un.klo + kt * kBN - a.key_row0;
                 tc5::mbar_expect_tx(full, kTileBytes);
+                if (a.block_table) {
+                    // a 128-key tile is two pages; a page past the sequence's last one holds only keys that every
+                    // query of the unit has masked, so any resident page stands in for it
+                    for (int rh = 0; rh < 2; rh++) {
+                        const int blk = (row >> 6) + rh;
+                        int page = blk < a.table_len ? __ldg(a.block_table + blk) : -1;
+                        if (page < 0) page = 0;
+                        const uint32_t d = dst + rh * (kTileBytes / 4);
+                        tc5::tma_load_3d(d, map, full, 0, 0, page * kNHeadKv + un.kvh);
+                        tc5::tma_load_3d(d + kTileBytes / 2, map, full, 64, 0, page * kNHeadKv + un.kvh);
+                    }
+                    return true;
+                }
                 tc5::tma_load_3d(dst, map, full, 0, row, un.kvh);
                 tc5::tma_load_3d(dst + kTileBytes / 2, map, full, 64, row, un.kvh);
                 return true;
@@ -849,6 +870,7 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     pa.q_st = q_st; pa.k_st = k_st; pa.v_st = v_st;
     pa.n_slots = p.n_slots; pa.is_swa = p.is_swa; pa.has_rope = p.has_rope; pa.qkv_dtype = p.qkv_dtype;
     pa.p0 = p.p0; pa.n_tok = T; pa.n_hist = n_hist;
+    pa.block_table = p.block_table;
     cudaError_t e;
     if (n_hist > 0) {
         pa.history_pass = 1;
@@ -869,8 +891,13 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     const void *kb = p.is_swa ? static_cast<const void *>(k_st) : static_cast<const void *>(p.k_cache);
     const void *vb = p.is_swa ? static_cast<const void *>(v_st) : static_cast<const void *>(p.v_cache);
     const int kv_rows = p.is_swa ? n_hist + T : p.n_slots;
-    if ((e = make_map(&tm_k, kb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
-    if ((e = make_map(&tm_v, vb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
+    if (p.block_table) {  // page pool: {128 dims, 64 rows of a page, pages x KV heads}, one 64-row box per load
+        if ((e = make_map(&tm_k, kb, 64, p.n_pages * kNHeadKv, 64, 1)) != cudaSuccess) return e;
+        if ((e = make_map(&tm_v, vb, 64, p.n_pages * kNHeadKv, 64, 1)) != cudaSuccess) return e;
+    } else {
+        if ((e = make_map(&tm_k, kb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
+        if ((e = make_map(&tm_v, vb, kv_rows, kNHeadKv, kBN, 1)) != cudaSuccess) return e;
+    }
 
     PfArgs a{};
     a.q_st = q_st;
@@ -880,6 +907,7 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
     a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
     a.n_ksplit = n_ksplit; a.t_pad = t_pad; a.part_ml = part_ml;
+    a.block_table = p.block_table; a.table_len = p.table_len;
     const int n_units = n_units_q * n_ksplit;
     const dim3 grid(n_units < g_sm_count ? n_units : g_sm_count);
     a.n_units = n_units;

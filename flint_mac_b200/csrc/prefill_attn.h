@@ -15,6 +15,10 @@ struct PrefillParams {
     int p0, n_tok;     // positions p0 .. p0+n_tok-1
     int qkv_dtype, out_dtype;
     cudaEvent_t ev_attn_begin = nullptr, ev_attn_end = nullptr;  // optional: recorded around the attention kernel alone
+    // Paged full-attention layer: k_cache / v_cache are the layer's page pools [n_pages][4][64][128] and block_table
+    // (device, this sequence's row) maps the 64-key block b to its page.
+    const int32_t *block_table = nullptr;
+    int n_pages = 0, table_len = 0;
 };
 
 // Device scratch that lives with the handle and grows on demand: half-precision staging of the normalised,

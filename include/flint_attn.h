@@ -54,6 +54,9 @@ typedef struct {
     int32_t n_ctx;                 /* context length per sequence (src/capi.h:16) */
     int32_t kv_rank;               /* KV-range sharding of full layers over devices: this shard ... */
     int32_t kv_ranks;              /* ... of this many (0 or 1: not sharded) */
+    int32_t kv_pages;              /* 0: every sequence owns n_ctx slots per full layer (src/engine.mm:509-511).
+                                      > 0: full layers keep K/V in a pool of this many 64-key pages per layer, handed to
+                                      sequences on demand through a block table (see flint_attn_seq_release) */
 } flint_attn_config;
 
 /* src/capi.h:20-21. NULL + message on failure. */
@@ -180,10 +183,26 @@ int32_t flint_attn_read_kv(flint_attn *a, int32_t layer, int32_t seq, int32_t sl
                            uint16_t *v, char *err, int32_t err_len);
 int32_t flint_attn_write_kv(flint_attn *a, int32_t layer, int32_t seq, int32_t slot0, int32_t n, const uint16_t *k,
                             const uint16_t *v, char *err, int32_t err_len);
-/* Device addresses of a layer's K (which = 0) or V (1) cache, for zero-copy fills by a co-resident producer. */
+/* Device addresses of a layer's K (which = 0) or V (1) cache, for zero-copy fills by a co-resident producer (the
+ * page pool [kv_pages][4][64][128] of a paged layer). */
 void *flint_attn_kv_dev(flint_attn *a, int32_t layer, int32_t which);
 /* Declare that a sequence's caches already hold `pos` tokens (after flint_attn_write_kv / a device-side fill). */
 int32_t flint_attn_set_pos(flint_attn *a, int32_t seq, int32_t pos);
+
+/* ---- paged KV cache: sequences that join and leave ------------------------------------------------------
+ * No counterpart in the reference, which serves one session from one contiguous cache (src/engine.mm:509-511,
+ * server/src/main.rs:84).  With kv_pages > 0 a full-attention layer's cache is a pool of 64-key pages (one decode
+ * tile each) shared by all max_seqs sequence slots; a sequence takes a page whenever its position enters a new
+ * 64-key block (in decode, prefill or flint_attn_write_kv; the call fails with "KV page pool exhausted" and changes
+ * nothing when none is free) and keeps its pages across flint_attn_truncate.  Sliding-window layers keep their
+ * 1024-slot ring per sequence slot.  A serving loop admits a request into a free slot, runs it, and retires it:
+ *   flint_attn_seq_release   position back to 0 and every page of the slot back to the pool.  Pages are reused by later
+ *                            launches: call it once the sequence's last launch is enqueued, and keep all launches of a
+ *                            handle on one stream (or synchronise) so that reuse stays ordered behind earlier readers.
+ *   flint_attn_pages_free    pages currently free (-1 when the handle is not paged).
+ * Results are the same as with contiguous caches; only where K/V rows live differs. */
+int32_t flint_attn_seq_release(flint_attn *a, int32_t seq);
+int32_t flint_attn_pages_free(const flint_attn *a);
 
 /* ---- host-side planning, exposed for tests (no GPU needed) -----------------------------------------
  * The split-K work list the decode launch would use for n tokens at positions pos[]: one record of 8 int32 per

@@ -53,10 +53,11 @@ def test_noalloc_decode_matches_handle_decode_twice_in_a_row(fo, kind):
                                   sk_d)
             torch.cuda.synchronize()
             # Same kernel and same inputs.  The handle may cut the key ranges a little differently (on the second call
-            # it extends its previous work list by one position instead of planning anew), so the two agree to the
-            # tolerance of the split-invariance test rather than bit for bit.
+            # it extends its previous work list by one position instead of planning anew), so the two agree to what
+            # moving a split boundary does to the half-precision probabilities (a few 1e-5), far inside the 2e-3 of
+            # the parity tests, rather than bit for bit.
             assert torch.isfinite(got).all()
-            assert (got - want).abs().max().item() <= 2e-5, f"call {call}: outputs differ from flint_attn_decode_dev"
+            assert (got - want).abs().max().item() <= 1e-4, f"call {call}: outputs differ from flint_attn_decode_dev"
             # both wrote the new token's K/V into its slot
             for s, p in enumerate(pos):
                 slot = fo.slot(p, is_swa)
