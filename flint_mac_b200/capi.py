@@ -64,6 +64,10 @@ SYMBOLS = {
                                                  C.c_char_p, C.c_int32]),
     "flint_attn_project_dev": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_prefill_partial_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int32,
+                                                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_char_p, C.c_int32]),
+    "flint_attn_prefill_combine_dev": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                   C.c_int32, C.c_void_p, C.c_char_p, C.c_int32]),
     "flint_attn_check": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32]),
     "flint_attn_n_slots": (C.c_int32, [C.c_void_p, C.c_int32]),
     "flint_attn_read_kv": (C.c_int32, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
@@ -332,6 +336,14 @@ class Attn:
     def project_dev(self, w_dev, n_rows_w, k, x_dev, n, norm_w_dev, out_dev, stream: int = 0):
         self._call("flint_attn_project_dev", _ptr(w_dev), n_rows_w, k, _ptr(x_dev), n,
                    _ptr(norm_w_dev) if norm_w_dev is not None else None, _ptr(out_dev), stream)
+
+    def prefill_partial_dev(self, layer, seq, n_tok, qkv_dev, qkv_dtype, partial_o_dev, partial_ml_dev, stream: int = 0):
+        self._call("flint_attn_prefill_partial_dev", layer, seq, n_tok, _ptr(qkv_dev), qkv_dtype, _ptr(partial_o_dev),
+                   _ptr(partial_ml_dev), stream)
+
+    def prefill_combine_dev(self, n_tok, n_parts, partials_o_dev, partials_ml_dev, out_dev, out_dtype, stream: int = 0):
+        self._call("flint_attn_prefill_combine_dev", n_tok, n_parts, _ptr(partials_o_dev), _ptr(partials_ml_dev),
+                   _ptr(out_dev), out_dtype, stream)
 
     def check(self):
         """Synchronise and raise if any asynchronous call of this handle failed on the device."""

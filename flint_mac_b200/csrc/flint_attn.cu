@@ -791,15 +791,19 @@ int32_t flint_attn_decode(flint_attn *a, int32_t layer, int32_t n, const int32_t
 }
 
 static void prefill_impl(flint_attn *a, int layer, int seq, int n_tok, const void *qkv, int qkv_dtype, void *out,
-                         int out_dtype, cudaStream_t st) {
+                         int out_dtype, cudaStream_t st, float *partial_o = nullptr, float *partial_ml = nullptr) {
     CK(cudaSetDevice(a->device));
     Layer &L = a->layer(layer);
     if (seq < 0 || seq >= a->max_seqs) throw std::runtime_error("sequence index out of range");
     if (n_tok <= 0) throw std::runtime_error("empty prefill");  // src/engine.mm:975
     const int p0 = a->pos[seq];
     if (p0 + n_tok > a->n_ctx) throw std::runtime_error("context full");  // src/engine.mm:976
-    if (a->kv_ranks > 1 && !L.is_swa) throw std::runtime_error("prefill of a KV-sharded full layer is not supported");
-    if ((qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) || (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16))
+    if (a->kv_ranks > 1 && !L.is_swa && !partial_o)
+        throw std::runtime_error("full layers of a KV-sharded handle need prefill_partial + prefill_combine");
+    if (partial_o && L.is_swa) throw std::runtime_error("sliding-window layers are not sharded: use prefill_dev");
+    if (partial_o && !partial_ml) throw std::runtime_error("null partial buffer");
+    if ((qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) ||
+        (!partial_o && out_dtype != kDtypeF32 && out_dtype != kDtypeBf16))
         throw std::runtime_error("bad dtype");
     PrefillParams pp{};
     pp.qkv = qkv; pp.out = out;
@@ -816,6 +820,13 @@ static void prefill_impl(flint_attn *a, int layer, int seq, int n_tok, const voi
     pp.n_slots = L.n_slots;
     pp.is_swa = L.is_swa; pp.has_rope = L.has_rope;
     pp.p0 = p0; pp.n_tok = n_tok;
+    if (!L.is_swa) {
+        pp.kv_lo = L.kv_lo;
+        pp.kv_hi = L.kv_hi;
+        pp.with_sink = a->kv_rank == 0;  // the shard that holds position 0 carries the sink
+    }
+    pp.partial_o = partial_o;
+    pp.partial_ml = partial_ml;
     int n_launch = 0;
     if (a->timing) {  // the attention kernel alone; the prologue is a separate, bandwidth-bound launch
         pp.ev_attn_begin = a->next_event();
@@ -869,6 +880,31 @@ int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_
                                int32_t err_len) {
     API_TRY
     prefill_impl(a, layer, seq, n_tok, qkv_dev, qkv_dtype, out_dev, out_dtype, cudaStream_t(cuda_stream));
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_prefill_partial_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv_dev,
+                                       int32_t qkv_dtype, float *partial_o_dev, float *partial_ml_dev, void *cuda_stream,
+                                       char *err, int32_t err_len) {
+    API_TRY
+    if (!partial_o_dev || !partial_ml_dev) throw std::runtime_error("null partial buffer");
+    prefill_impl(a, layer, seq, n_tok, qkv_dev, qkv_dtype, nullptr, kDtypeF32, cudaStream_t(cuda_stream), partial_o_dev,
+                 partial_ml_dev);
+    return 0;
+    API_CATCH(-1)
+}
+
+int32_t flint_attn_prefill_combine_dev(flint_attn *a, int32_t n_tok, int32_t n_parts, const float *partials_o_dev,
+                                       const float *partials_ml_dev, void *out_dev, int32_t out_dtype, void *cuda_stream,
+                                       char *err, int32_t err_len) {
+    API_TRY
+    CK(cudaSetDevice(a->device));
+    if (n_tok <= 0 || n_parts <= 0 || !partials_o_dev || !partials_ml_dev || !out_dev)
+        throw std::runtime_error("bad combine shape");
+    if (out_dtype != kDtypeF32 && out_dtype != kDtypeBf16) throw std::runtime_error("bad out dtype");
+    CK(launch_prefill_combine(partials_o_dev, partials_ml_dev, n_parts, n_tok, out_dev, out_dtype, cudaStream_t(cuda_stream)));
+    a->launches++;
     return 0;
     API_CATCH(-1)
 }

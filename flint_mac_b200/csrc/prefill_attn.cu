@@ -81,6 +81,9 @@ struct PfArgs {
     // the sequence is page block_table[b] (entries past the sequence's last page are negative)
     const int32_t *block_table;
     int table_len;
+    // Key-range shard of a full layer (context-parallel prefill): this device holds keys [kr_lo, kr_hi) only; a unit's
+    // keys are clipped to it, the sink enters on the device that says so, and the output is an un-normalised partial.
+    int kr_lo, kr_hi, with_sink, cp_partial;
 };
 
 // ------------------------------------------------------------------------------------------------- prologue
@@ -94,6 +97,7 @@ struct PrologueArgs {
     int p0, n_tok, n_hist;
     int history_pass;  // 1: only copy the history rows out of the ring; 0: only the new tokens
     const int32_t *block_table;  // paged full layer: k_cache / v_cache are page pools, slot = page * 64 + pos % 64
+    int kv_lo, kv_hi;            // full layer: positions this device's cache holds (slot = pos - kv_lo); others are not stored
 };
 
 __device__ __forceinline__ float4 pf_load_row4(const void *base, int dtype, size_t elem0, int lane) {
@@ -172,7 +176,8 @@ __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) 
         return;
     }
     const float4 wk = reinterpret_cast<const float4 *>(a.k_norm)[lane];
-    const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos;  // prefill.metal:106
+    const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos - a.kv_lo;  // prefill.metal:106
+    const bool mine = a.is_swa || (pos >= a.kv_lo && pos < a.kv_hi);
     // paged layer: [page][kv head][64 slots][128] instead of [kv head][slot][128]
     const size_t page = a.block_table ? size_t(a.block_table[pos >> 6]) : 0;
 #pragma unroll
@@ -182,7 +187,7 @@ __global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) 
         const float4 y = is_k ? pf_norm_rope(x[i], wk, cs, sn, lane, a.has_rope != 0) : x[i];
         // On a ring layer tokens t and t + 1024 of one launch share a slot: only the last token that maps to a slot
         // stores there, so the ring's final contents do not depend on the order in which the CTAs run.
-        if (!a.is_swa || t + kSwaRing >= a.n_tok) {
+        if (mine && (!a.is_swa || t + kSwaRing >= a.n_tok)) {
             __half *cache = is_k ? a.k_cache : a.v_cache;
             const size_t row = a.block_table ? (page * kNHeadKv + kvh) * 64 + (pos & 63) : size_t(kvh) * a.n_slots + slot;
             pf_store_half4(cache + row * kHeadDim + 4 * lane, y);
@@ -237,7 +242,8 @@ struct Unit {
 // Units are handed out longest first: late query blocks (full 544-key bands) before the first 16 blocks of the
 // prompt, whose bands are shorter, so that the CTAs that get one unit more than the others get short ones.
 // (Host and device: the host's schedule uses the same tile counts.)
-__host__ __device__ inline Unit unit_geom_of(int u, int n_tok, int p0, int is_swa, int key_row0, int n_ksplit) {
+__host__ __device__ inline Unit unit_geom_of(int u, int n_tok, int p0, int is_swa, int key_row0, int n_ksplit,
+                                             int kr_lo = 0, int kr_hi = 0x7fffffff) {
     Unit g;
     const int uq = u / n_ksplit;
     g.split = u % n_ksplit;
@@ -248,8 +254,8 @@ __host__ __device__ inline Unit unit_geom_of(int u, int n_tok, int p0, int is_sw
     const int t_end = g.t0 + kCtaPos < n_tok ? g.t0 + kCtaPos : n_tok;
     g.q_last = p0 + t_end - 1;
     const int lo_swa = g.q_first - kHist > key_row0 ? g.q_first - kHist : key_row0;
-    g.klo = is_swa ? lo_swa : 0;
-    g.n_keys = g.q_last - g.klo + 1;
+    g.klo = is_swa ? lo_swa : (kr_lo > 0 ? kr_lo : 0);
+    g.n_keys = (is_swa || g.q_last < kr_hi ? g.q_last + 1 : kr_hi) - g.klo;  // <= 0: the unit has no key on this device
     g.n_tiles = (g.n_keys + kBN - 1) / kBN;
     if (n_ksplit > 1) {  // the host guarantees at least 4 tiles per range; the last range takes the remainder
         const int per = g.n_tiles / n_ksplit;
@@ -262,7 +268,7 @@ __host__ __device__ inline Unit unit_geom_of(int u, int n_tok, int p0, int is_sw
     return g;
 }
 __device__ __forceinline__ Unit unit_geom(const PfArgs &a, int u) {
-    return unit_geom_of(u, a.n_tok, a.p0, a.is_swa, a.key_row0, a.n_ksplit);
+    return unit_geom_of(u, a.n_tok, a.p0, a.is_swa, a.key_row0, a.n_ksplit, a.kr_lo, a.kr_hi);
 }
 
 // The i-th unit of this CTA, or -1.  The host balances the units over the CTAs by their tile counts and lays each
@@ -493,7 +499,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
 
         // prefill.metal:162: the sink enters through m0 = sink, l0 = 1 -- once per row, so with a split key range
         // only the first range carries it (the others start empty; their first tile is fully visible, so m gets finite)
-        const bool has_sink = un.split == 0;
+        const bool has_sink = un.split == 0 && a.with_sink;
         float m = has_sink ? sink2 : -INFINITY, l = has_sink ? 1.0f : 0.0f;
         for (int kt = 0; kt < n_tiles && ok; kt++) {
             ok = __all_sync(0xffffffffu, wait_bar(bar(kBarSReady + w), j & 1));  // warp-uniform for tcgen05.ld
@@ -502,15 +508,17 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             const int kbase = klo + kt * kBN;
             const int n_cols = min(kBN, (n_keys - kt * kBN + 15) & ~15);  // columns the MMA wrote (same as the issuer)
             const int n_chunks = (n_cols + 31) >> 5;
-            // visible columns of this row form one range [c_lo, c_hi] (prefill.metal:212)
-            const int c_hi = qpos - kbase;
+            // visible columns of this row form one range [c_lo, c_hi] (prefill.metal:212); on a key-range shard the
+            // unit's keys also end with the shard (k_end), before the causal limit of later queries
+            const int k_end = klo + n_keys - 1;
+            const int c_hi = min(qpos, k_end) - kbase;
             const int c_lo = a.is_swa ? qpos - kHist - kbase : -(1 << 30);
             // Per 32-column chunk, for the whole Q tile: 0 = every row sees every key (no per-element mask),
             // 1 = mixed, 2 = no row sees any key.  Only the two ends of the band are mixed.
             auto chunk_kind = [&](int ch) {
                 const int key_lo = kbase + ch * 32, key_hi = key_lo + 31;
-                if (key_lo > qt_last || (a.is_swa && key_hi < qt_first - kHist)) return 2;
-                if (key_hi <= qt_first && (!a.is_swa || key_lo >= qt_last - kHist)) return 0;
+                if (key_lo > qt_last || key_lo > k_end || (a.is_swa && key_hi < qt_first - kHist)) return 2;
+                if (key_hi <= qt_first && key_hi <= k_end && (!a.is_swa || key_lo >= qt_last - kHist)) return 0;
                 return 1;
             };
 
@@ -588,6 +596,9 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             }
             // probabilities: P (half) goes to this Q tile's shared-memory block in the K-major 128-byte-swizzled layout
             // of an MMA A operand: two 64-key halves of [128 rows][128 B]
+            // A row that has not seen a visible key yet (a key-range shard that starts after its position) still has
+            // m = -inf: its scores are all -inf, and against a finite stand-in they give p = 0 instead of a NaN.
+            const float mref = m == -INFINITY ? 0.0f : m;
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int ch = 0; ch < kBN / 32; ch++) {
@@ -595,10 +606,10 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                     uint32_t pw[16];
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
-                        const float p0 = fast_exp2(__uint_as_float(sr[ch * 32 + c]) - m);
-                        const float p1 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 1]) - m);
-                        const float p2 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 2]) - m);
-                        const float p3 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 3]) - m);
+                        const float p0 = fast_exp2(__uint_as_float(sr[ch * 32 + c]) - mref);
+                        const float p1 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 1]) - mref);
+                        const float p2 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 2]) - mref);
+                        const float p3 = fast_exp2(__uint_as_float(sr[ch * 32 + c + 3]) - mref);
                         sum[0] += p0; sum[1] += p1; sum[2] += p2; sum[3] += p3;
                         pw[c >> 1] = pack_half2(p0, p1);
                         pw[(c >> 1) + 1] = pack_half2(p2, p3);
@@ -625,7 +636,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             // the blocks to TMA, which writes full lines and clips rows past the prompt.  bf16 rows fit the two staging
             // blocks at once; fp32 rows go out in two rounds.  The TMA store of a unit drains while the next unit runs.
             tc5::fence_after_sync();
-            const bool partial = a.n_ksplit > 1;
+            const bool partial = a.n_ksplit > 1 || a.cp_partial;
             const float inv_l = partial ? 1.0f : 1.0f / l;
             const bool f32 = a.out_dtype == kDtypeF32;
             const int row0 = un.t0 + w * kQPos + un.split * a.t_pad;  // row of the output tensor this Q tile starts at
@@ -701,22 +712,29 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
 // Merge of the key-range partials of one chunk: out[t][head][:] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
 // (the log-sum-exp merge of src/metal/fused.metal:332-350 applied to prefill rows; the sink is inside range 0's l).
 // One CTA per (token, 4 heads), thread = (head, 4 dims).
+// With ml_out the result stays a partial: the un-normalised sum at the common maximum and its (M, L), for a later
+// merge with the other devices' partials.
 __global__ void __launch_bounds__(128) k_prefill_merge(const float *part_o, const float2 *part_ml, void *out, int out_dtype,
-                                                       int n_tok, int t_pad, int n_ksplit) {
+                                                       int n_tok, int t_pad, int n_ksplit, float2 *ml_out) {
     const int t = blockIdx.x / (kNHead / 4);
     const int head = (blockIdx.x % (kNHead / 4)) * 4 + (threadIdx.x >> 5);
     const int d = (threadIdx.x & 31) * 4;
     float M = -INFINITY;
-    for (int s = 0; s < n_ksplit; s++) M = fmaxf(M, part_ml[(size_t(s) * t_pad + t) * kNHead + head].x);
+    for (int s = 0; s < n_ksplit; s++) {
+        const float2 ml = part_ml[(size_t(s) * t_pad + t) * kNHead + head];
+        if (ml.y != 0.f) M = fmaxf(M, ml.x);
+    }
     float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < n_ksplit; s++) {
         const float2 ml = part_ml[(size_t(s) * t_pad + t) * kNHead + head];
-        const float c = ml.y == 0.f ? 0.f : exp2f(ml.x - M);
+        if (ml.y == 0.f) continue;  // an empty part (no key of this row in the range): its rows were never written
+        const float c = exp2f(ml.x - M);
         const float4 o = *reinterpret_cast<const float4 *>(part_o + (size_t(s) * t_pad + t) * kQDim + head * kHeadDim + d);
         L += ml.y * c;
         acc[0] += o.x * c; acc[1] += o.y * c; acc[2] += o.z * c; acc[3] += o.w * c;
     }
-    const float inv = 1.0f / L;
+    const float inv = ml_out ? 1.0f : 1.0f / L;
+    if (ml_out && d == 0) ml_out[size_t(t) * kNHead + head] = make_float2(L == 0.f ? 0.f : M, L);
     const size_t idx = size_t(t) * kQDim + head * kHeadDim + d;
     if (out_dtype == kDtypeF32) {
         *reinterpret_cast<float4 *>(static_cast<float *>(out) + idx) =
@@ -768,13 +786,13 @@ cudaError_t make_out_map(CUtensorMap *map, void *base, int n_tok, int out_dtype)
 // tiles than others.  Greedy longest-first assignment to the least loaded CTA by (key tiles + one tile of per-unit
 // overhead); unit indices are already ordered longest first.  The table is kept until the geometry changes.
 cudaError_t build_schedule(PrefillWorkspace &ws, const PfArgs &a, int n_units, int grid, cudaStream_t stream) {
-    const int key[5] = {a.n_tok, a.p0, a.is_swa * 256 + a.n_ksplit, a.key_row0, grid};
+    const int key[5] = {a.n_tok, a.p0, a.is_swa * 256 + a.n_ksplit, a.key_row0 ^ (a.kr_hi * 31), grid};
     if (ws.sched && memcmp(key, ws.sched_key, sizeof(key)) == 0) return cudaSuccess;
     std::vector<std::vector<int>> lists(grid);
     std::priority_queue<std::pair<int, int>, std::vector<std::pair<int, int>>, std::greater<std::pair<int, int>>> heap;
     for (int b = 0; b < grid; b++) heap.push({0, b});
     for (int u = 0; u < n_units; u++) {
-        const int tiles = unit_geom_of(u, a.n_tok, a.p0, a.is_swa, a.key_row0, a.n_ksplit).n_tiles;
+        const int tiles = unit_geom_of(u, a.n_tok, a.p0, a.is_swa, a.key_row0, a.n_ksplit, a.kr_lo, a.kr_hi).n_tiles;
         const auto [load, b] = heap.top();
         heap.pop();
         lists[b].push_back(u);
@@ -834,10 +852,22 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     // Key-range split: a chunk on a full layer with fewer units than SMs and a long history leaves most of the GPU
     // idle (512 tokens = 64 units) while every unit walks hundreds of key tiles.  Each unit is then cut into ranges
     // of at least 4 key tiles, as many as fit the SMs, and a small kernel merges the partials.
-    const int n_units_q = ((T + kCtaPos - 1) / kCtaPos) * kNHeadKv;
+    // A key-range shard [kv_lo, kv_hi) of a full layer only has work for query blocks that end at or after kv_lo.
+    // Units are numbered from the last query block down, so those form a prefix of the numbering.
+    const bool cp = p.partial_o != nullptr;
+    const int kr_lo = p.is_swa ? 0 : p.kv_lo, kr_hi = p.is_swa ? 0x7fffffff : p.kv_hi;
+    const int n_qb = (T + kCtaPos - 1) / kCtaPos;
+    // (the last block ends at p0 + T - 1; if even that lies before kv_lo, no block has a key here)
+    const int first_block = p.p0 + T - 1 < kr_lo ? n_qb : std::max(0, (kr_lo - p.p0) / kCtaPos);
+    const int n_units_q = (n_qb - first_block) * kNHeadKv;
+    // every unit handed to the kernel must own at least one key: a unit without keys would issue products of width 0
+    if (n_units_q > 0 && (unit_geom_of(n_units_q - 1, T, p.p0, p.is_swa, p.is_swa ? p.p0 - n_hist : kr_lo, 1, kr_lo, kr_hi).n_keys <= 0 ||
+                          unit_geom_of(0, T, p.p0, p.is_swa, p.is_swa ? p.p0 - n_hist : kr_lo, 1, kr_lo, kr_hi).n_keys <= 0))
+        return cudaErrorInvalidValue;
     int n_ksplit = 1;
-    if (!p.is_swa && n_units_q * 2 <= g_sm_count) {
-        const int min_tiles = (p.p0 + (T < kCtaPos ? T : kCtaPos) + kBN - 1) / kBN;  // the first query block's tiles
+    if (!p.is_swa && n_units_q > 0 && n_units_q * 2 <= g_sm_count) {
+        // the shortest unit's tiles (the first query block that has keys here)
+        const int min_tiles = unit_geom_of(n_units_q - 1, T, p.p0, 0, 0, 1, kr_lo, kr_hi).n_tiles;
         n_ksplit = std::max(1, std::min(g_sm_count / n_units_q, min_tiles / 4));
     }
     const int t_pad = (T + kCtaPos - 1) / kCtaPos * kCtaPos;
@@ -871,6 +901,8 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     pa.n_slots = p.n_slots; pa.is_swa = p.is_swa; pa.has_rope = p.has_rope; pa.qkv_dtype = p.qkv_dtype;
     pa.p0 = p.p0; pa.n_tok = T; pa.n_hist = n_hist;
     pa.block_table = p.block_table;
+    pa.kv_lo = p.is_swa ? 0 : p.kv_lo;
+    pa.kv_hi = p.is_swa ? 0x7fffffff : p.kv_hi;
     cudaError_t e;
     if (n_hist > 0) {
         pa.history_pass = 1;
@@ -883,8 +915,13 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     if ((e = cudaGetLastError()) != cudaSuccess) return e;
     (*n_launches)++;
 
+    if (cp) {  // rows whose unit has no key on this device are never written: they must read as empty parts
+        if ((e = cudaMemsetAsync(p.partial_ml, 0, size_t(T) * kNHead * sizeof(float2), stream)) != cudaSuccess) return e;
+        if (n_units_q == 0) return cudaSuccess;
+    }
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
     if (n_ksplit > 1) e = make_out_map(&tm_o, part_o, n_ksplit * t_pad, kDtypeF32);  // partials: fp32, un-normalised
+    else if (cp) e = make_out_map(&tm_o, p.partial_o, T, kDtypeF32);
     else e = make_out_map(&tm_o, p.out, T, p.out_dtype);
     if (e != cudaSuccess) return e;
     if ((e = make_map(&tm_q, q_st, T, kNHead, kQPos, kGqa)) != cudaSuccess) return e;
@@ -901,12 +938,16 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
 
     PfArgs a{};
     a.q_st = q_st;
-    a.out = n_ksplit > 1 ? static_cast<void *>(part_o) : p.out;
+    a.out = n_ksplit > 1 ? static_cast<void *>(part_o) : cp ? static_cast<void *>(p.partial_o) : p.out;
     a.sinks = p.sinks; a.error_flag = err_flag;
-    a.out_dtype = n_ksplit > 1 ? kDtypeF32 : p.out_dtype;
+    a.out_dtype = n_ksplit > 1 || cp ? kDtypeF32 : p.out_dtype;
     a.p0 = p.p0; a.n_tok = T; a.is_swa = p.is_swa;
-    a.key_row0 = p.is_swa ? p.p0 - n_hist : 0;
-    a.n_ksplit = n_ksplit; a.t_pad = t_pad; a.part_ml = part_ml;
+    a.key_row0 = p.is_swa ? p.p0 - n_hist : kr_lo;  // row 0 of a full layer's cache holds position kv_lo
+    a.n_ksplit = n_ksplit; a.t_pad = t_pad;
+    a.part_ml = n_ksplit > 1 ? part_ml : cp ? reinterpret_cast<float2 *>(p.partial_ml) : part_ml;
+    a.kr_lo = kr_lo; a.kr_hi = kr_hi;
+    a.with_sink = p.with_sink;
+    a.cp_partial = cp ? 1 : 0;
     a.block_table = p.block_table; a.table_len = p.table_len;
     const int n_units = n_units_q * n_ksplit;
     const dim3 grid(n_units < g_sm_count ? n_units : g_sm_count);
@@ -926,12 +967,22 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     if (e != cudaSuccess) return e;
     (*n_launches)++;
     if (n_ksplit > 1) {
-        k_prefill_merge<<<unsigned(T) * (kNHead / 4), 128, 0, stream>>>(part_o, part_ml, p.out, p.out_dtype, T, t_pad, n_ksplit);
+        k_prefill_merge<<<unsigned(T) * (kNHead / 4), 128, 0, stream>>>(
+            part_o, part_ml, cp ? static_cast<void *>(p.partial_o) : p.out, cp ? kDtypeF32 : p.out_dtype, T, t_pad, n_ksplit,
+            cp ? reinterpret_cast<float2 *>(p.partial_ml) : nullptr);
         if ((e = cudaGetLastError()) != cudaSuccess) return e;
         (*n_launches)++;
     }
     if (p.ev_attn_end) cudaEventRecord(p.ev_attn_end, stream);
     return cudaSuccess;
+}
+
+cudaError_t launch_prefill_combine(const float *parts_o, const float *parts_ml, int n_parts, int n_tok, void *out,
+                                   int out_dtype, cudaStream_t stream) {
+    if (n_tok <= 0 || n_parts <= 0) return cudaSuccess;
+    k_prefill_merge<<<unsigned(n_tok) * (kNHead / 4), 128, 0, stream>>>(parts_o, reinterpret_cast<const float2 *>(parts_ml), out,
+                                                                     out_dtype, n_tok, n_tok, n_parts, nullptr);
+    return cudaGetLastError();
 }
 
 cudaError_t prefill_error_flag(const PrefillWorkspace &ws, int *flag) {

@@ -19,6 +19,14 @@ struct PrefillParams {
     // (device, this sequence's row) maps the 64-key block b to its page.
     const int32_t *block_table = nullptr;
     int n_pages = 0, table_len = 0;
+    // Full layer whose cache holds positions [kv_lo, kv_hi) only (row 0 = position kv_lo).  with_sink: this device
+    // adds the learned sink (exactly one of the devices sharing a sequence does).
+    int kv_lo = 0, kv_hi = 0x7fffffff, with_sink = 1;
+    // Context-parallel prefill: instead of normalised rows in `out`, write this device's partial -- un-normalised
+    // fp32 rows [n_tok][4096] and per (token, head) the pair (m in base-2 units, l), [n_tok][32][2] -- for
+    // launch_prefill_combine after the devices have exchanged them.
+    float *partial_o = nullptr;
+    float *partial_ml = nullptr;
 };
 
 // Device scratch that lives with the handle and grows on demand: half-precision staging of the normalised,
@@ -36,6 +44,10 @@ struct PrefillWorkspace {
 cudaError_t prefill_kernel_setup();
 cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStream_t stream, int *n_launches);
 void prefill_workspace_free(PrefillWorkspace &ws);
+// parts_o [n_parts][n_tok][4096] fp32, parts_ml [n_parts][n_tok][32][2] -> out [n_tok][4096]: log-sum-exp merge of the
+// devices' partials (src/metal/fused.metal:332-350 applied to prefill rows; the sink is inside one part's l).
+cudaError_t launch_prefill_combine(const float *parts_o, const float *parts_ml, int n_parts, int n_tok, void *out,
+                                   int out_dtype, cudaStream_t stream);
 // Reads the device-side error word of the last prefill launches (0 = none; 1 = a bounded wait ran out; 2 = shared
 // memory was not 1024-byte aligned).  Blocking.  A non-zero word is cleared after it has been read.
 cudaError_t prefill_error_flag(const PrefillWorkspace &ws, int *flag);

@@ -143,6 +143,21 @@ int32_t flint_attn_prefill_dev(flint_attn *a, int32_t layer, int32_t seq, int32_
                                int32_t qkv_dtype, void *out_dev, int32_t out_dtype, void *cuda_stream, char *err,
                                int32_t err_len);
 
+/* ---- context-parallel prefill: a full layer whose key range is sharded over devices (kv_ranks > 1) -------------
+ * The reference prefills on one device (its own note on the cost of long full-attention prompts: docs/DEVLOG.md:192).
+ * Here every rank gets the same n_tok rows; each stores the K/V of the positions in its own range, attends all n_tok
+ * queries to the keys it holds and returns a partial: un-normalised fp32 rows partial_o [n_tok][4096] and, per
+ * (token, head), the pair (m in base-2 units, l) in partial_ml [n_tok][32][2]; the rank that holds position 0 adds
+ * the sink.  After an all-gather of both arrays (rank-major), prefill_combine merges them by log-sum-exp
+ * (src/metal/fused.metal:332-350 applied to prefill rows).  Sliding-window layers of such a handle are replicated
+ * and use flint_attn_prefill_dev on every rank.  Works on an unsharded handle too (one part). */
+int32_t flint_attn_prefill_partial_dev(flint_attn *a, int32_t layer, int32_t seq, int32_t n_tok, const void *qkv_dev,
+                                       int32_t qkv_dtype, float *partial_o_dev, float *partial_ml_dev, void *cuda_stream,
+                                       char *err, int32_t err_len);
+int32_t flint_attn_prefill_combine_dev(flint_attn *a, int32_t n_tok, int32_t n_parts, const float *partials_o_dev,
+                                       const float *partials_ml_dev, void *out_dev, int32_t out_dtype, void *cuda_stream,
+                                       char *err, int32_t err_len);
+
 /* ---- the attention block with its projections ---------------------------------------------------------
  * The steps either side of attention in the reference engine: the q/k/v matvecs on the attn_norm-ed residual stream
  * (src/engine.mm:728-732; fused form k_qkv, src/metal/fused.metal:215-231) and the o-proj matvec with the residual

@@ -253,3 +253,61 @@ def test_rollback_and_recompute(fa, fo):
             redo = np.empty((T - restart, 4096), np.float32)
             h.prefill(0, 0, T - restart, np.ascontiguousarray(qkv[restart:]), fa.F32, redo, fa.F32)
             assert_close(redo[p - restart:], want[p:], f"rollback by {back}")
+
+
+@pytest.mark.parametrize("n_ctx,chunks", [(1008, [700, 300]), (4108, [512, 1500, 37, 2000])])
+def test_context_parallel_prefill_of_a_kv_sharded_full_layer(fa, fo, n_ctx, chunks):
+    """A full layer whose key range is cut over two ranks (two handles on this GPU): every rank gets the same rows,
+    stores the K/V of its own positions, attends all queries to the keys it holds and returns an un-normalised partial
+    with (m, l) per row; the merged result equals the reference arithmetic, chunk after chunk (the second rank has no
+    key at all for early chunks, a few for the chunk that crosses the boundary), and a decode step through the
+    sharded decode path on the caches the prefill built agrees too."""
+    import torch
+
+    seed, T = 61, sum(chunks)
+    w = fo.layer_weights(seed, 1)
+    qkv = fo.raw_qkv(seed, 1, 0, T + 1)
+    want, kc, vc = fo.layer_forward(qkv, *w, False, True, n_threads=8)
+    handles = [fa.Attn([False], [True], 1, n_ctx, kv_rank=r, kv_ranks=2) for r in range(2)]
+    try:
+        for h in handles:
+            h.set_layer(0, *w)
+        with pytest.raises(fa.FlintAttnError, match="prefill_partial"):
+            handles[0].prefill(0, 0, 8, np.ascontiguousarray(qkv[:8]), fa.F32, np.empty((8, 4096), np.float32), fa.F32)
+        p0 = 0
+        for n in chunks:
+            rows = torch.from_numpy(np.ascontiguousarray(qkv[p0:p0 + n])).cuda()
+            po = torch.full((2, n, 4096), float("nan"), device="cuda")
+            pml = torch.full((2, n, 32, 2), float("nan"), device="cuda")
+            for r, h in enumerate(handles):
+                h.prefill_partial_dev(0, 0, n, rows, fa.F32, po[r], pml[r])
+            out = torch.empty(n, 4096, device="cuda")
+            handles[1].prefill_combine_dev(n, 2, po, pml, out, fa.F32)
+            torch.cuda.synchronize()
+            for h in handles:
+                h.check()
+                h.advance([0], n)
+            assert_close(out.cpu().numpy(), want[p0:p0 + n], f"chunk at {p0} (+{n})")
+            shard = handles[0].n_slots(0)
+            if p0 + n <= shard:  # nothing of this chunk lies in the second rank's range: its partial is empty
+                assert float(pml[1, :, :, 1].abs().max()) == 0.0
+            p0 += n
+        # the caches the sharded prefill left behind: V bit-exact in the slot of its position, on the rank that owns it
+        shard = handles[0].n_slots(0)
+        for r, h in enumerate(handles):
+            lo, hi = r * shard, min(T, (r + 1) * shard)
+            if hi > lo:
+                _, v_dev = h.read_kv(0, 0, 0, hi - lo)
+                assert np.array_equal(v_dev.transpose(1, 0, 2).reshape(hi - lo, 512), fo.to_f16_bits(vc[lo:hi]))
+        # one decode step on top, through the sharded decode path
+        row = torch.from_numpy(np.ascontiguousarray(qkv[T:T + 1])).cuda()
+        parts = torch.zeros(2, 1, 32, 130, device="cuda")
+        for r, h in enumerate(handles):
+            h.decode_partial_dev(0, [0], row, fa.F32, parts[r])
+        dec = torch.empty(1, 4096, device="cuda")
+        handles[0].combine_dev(0, 1, 2, parts, dec, fa.F32)
+        torch.cuda.synchronize()
+        assert_close(dec.cpu().numpy()[0], want[T], "decode after the sharded prefill")
+    finally:
+        for h in handles:
+            h.close()
