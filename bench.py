@@ -425,7 +425,10 @@ def run_decode(args):
     hbm_peak, _, peak_kind = measured_peaks()
     total_steps = args.warmup + args.steps
     # strong scaling: the 64 sequences in contiguous blocks, one per rank
-    b0, b1 = shard.contiguous_blocks(N_SEQ, world)[rank]
+    # --emulate-world N (single GPU only): run rank 0's block of an N-way sharding, to look at the per-GPU step of a
+    # multi-GPU run without the other GPUs; the line then counts this block only
+    place_world = args.emulate_world if (world == 1 and args.emulate_world > 1) else world
+    b0, b1 = shard.contiguous_blocks(N_SEQ, place_world)[rank]
     n_loc = b1 - b0
     block_kv = n_loc * CTX * KV_BYTES_PER_KEY
     copies = max(1, -(-4 * L2_BYTES // block_kv))  # the copies together are at least four times L2
@@ -479,7 +482,9 @@ def run_decode(args):
             "dtype": "f16 KV, f16 tensor-core products, f32 accumulate/softmax", "data": "synthetic",
             "config": decode_config(world),
             "seqs_per_gpu": n_loc, "kv_copies_rotated": copies,
-            "tok_per_s": N_SEQ / (strong["ms_per_step"] * 1e-3),
+            **({"emulated": f"rank 0's block of a {place_world}-way sharding on one GPU; value counts this block only"}
+               if place_world != world else {}),
+            "tok_per_s": (n_loc if place_world != world else N_SEQ) / (strong["ms_per_step"] * 1e-3),
             "pct_of_hbm_peak": 100.0 * strong["value"] / world / hbm_peak,
             "roofline": {"bound": "hbm", "achieved": strong["achieved"], "peak": hbm_peak, "unit": "GB/s",
                          "frac": strong["achieved"] / hbm_peak, "traffic": traffic, "traffic_source": traffic_source,
@@ -530,6 +535,83 @@ def run_prefill_only(args):
                     "d2h_bytes_per_step": pf["d2h_bytes_per_step"], "us_per_step": pf["e2e_us"]},
             "gpu_launches": pf["gpu_launches_per_step"] * args.steps, "tok_per_s": pf["tok_per_s"], "clocks": clk.summary()}
     print(json.dumps(line), flush=True)
+
+
+def run_block(args):
+    """`--workload block`: the attention block with its projections on the decode batch -- 64 sequences x 8192 cached
+    tokens, hidden 4096: qkv = W_qkv . rmsnorm(x) (bf16 weights, 5120 x 4096), decode attention, x += W_o . att
+    (4096 x 4096).  The projections are bound by their weight stream: the line reports each against the HBM peak."""
+    import torch
+
+    import flint_mac_b200 as fa
+
+    rank, world, local = dist_setup(args.gpus)
+    if rank != 0:
+        return
+    hbm_peak, _, peak_kind = measured_peaks()
+    E, B = 4096, N_SEQ
+    total = args.warmup + args.steps
+    h = open_decode_handle(torch, fa, local, B, 1, total, 777)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    rng = np.random.default_rng(5)
+
+    def bf16(shape):
+        return (torch.randn(*shape, generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+
+    wq, wk, wv, wo = bf16((4096, E)), bf16((512, E)), bf16((512, E)), bf16((E, 4096))
+    h.set_projections(0, (1 + 0.1 * rng.standard_normal(E)).astype(np.float32),
+                      *(w.view(torch.int16).cpu().numpy().view(np.uint16) for w in (wq, wk, wv, wo)))
+    w_qkv = torch.cat([wq, wk, wv]).contiguous()
+    x = torch.randn(B, E, generator=gen, device="cuda")
+    nw = torch.ones(E, device="cuda")
+    qkv = torch.empty(B, QKV_DIM, device="cuda")
+    att = torch.randn(B, OUT_DIM, generator=gen, device="cuda")
+    o = torch.empty(B, E, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    seqs = fa.i32_array(list(range(B)))
+
+    def timed(fn, n):
+        ts = []
+        for i in range(args.warmup + n):
+            flush.fill_(i & 0xFF)  # the weights (33-42 MB) would otherwise sit in L2
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            if i >= args.warmup:
+                ts.append((e0, e1))
+        torch.cuda.synchronize()
+        return float(np.median([a.elapsed_time(b) for a, b in ts])) * 1e3
+
+    n = min(args.steps, 100)
+    qkv_us = timed(lambda: h.project_dev(w_qkv, QKV_DIM, E, x, B, nw, qkv, stream), n)
+    o_us = timed(lambda: h.project_dev(wo, E, 4096, att, B, None, o, stream), n)
+    for s in range(B):
+        h.set_pos(s, CTX)
+
+    def block():
+        h.decode_block_dev(0, seqs, x, stream)
+
+    block_us = timed(block, n)  # positions do not advance: every repetition is the same step
+    h.check()
+    qkv_bytes, o_bytes = QKV_DIM * E * 2, E * 4096 * 2
+    act_bytes = B * (E * 4 + QKV_DIM * 4)
+    line = {"metric": "attn_block_us", "value": block_us, "unit": "us", "n_gpus": 1, "steps": n, "warmup": args.warmup,
+            "ms_per_step": block_us * 1e-3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 weights, fp32 accumulate (activations as bf16 high + low parts), f16 KV", "data": "synthetic",
+            "config": {"workload": "attention block on the decode batch: 64 seqs x 8192 cached tokens, hidden 4096, "
+                                   "qkv projection with fused RMSNorm + decode attention + o-projection with residual",
+                       "l2": "flushed between repetitions (256 MiB write)"},
+            "roofline": {"bound": "hbm", "achieved": qkv_bytes / (qkv_us * 1e-6) / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": qkv_bytes / (qkv_us * 1e-6) / 1e9 / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "kernel": "k_proj (qkv projection, 64 rows; the activation split kernel included)",
+                         "kernel_us": qkv_us, "bytes_per_launch": qkv_bytes},
+            "o_proj": {"us": o_us, "gbs": o_bytes / (o_us * 1e-6) / 1e9, "frac": o_bytes / (o_us * 1e-6) / 1e9 / hbm_peak,
+                       "bytes_per_launch": o_bytes},
+            "activation_bytes_per_step": act_bytes, "gpu_launches": 5 * n}
+    print(json.dumps(line), flush=True)
+    h.close()
 
 
 def run_longctx(args):
@@ -778,14 +860,14 @@ def main():
     ap.add_argument("--steps", type=int, default=500)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "ragged"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "longctx", "ragged", "block"])
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_T, help="prefill workload: prompt length")
     ap.add_argument("--prefill-history", type=int, default=0,
                     help="prefill workload: tokens already cached before the timed chunk (chunked prefill)")
     ap.add_argument("--prefill-kind", default="swa", choices=["swa", "full"],
                     help="prefill workload: sliding-window ring layer (the configuration the metric is quoted on) or full attention")
     ap.add_argument("--emulate-world", type=int, default=1,
-                    help="ragged workload on one GPU: run rank 0's share of an N-way placement")
+                    help="decode / ragged workload on one GPU: run rank 0's share of an N-way placement")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="longctx on several GPUs: partial records through peer memory by the kernels, or by NCCL")
     ap.add_argument("--skip-prefill", action="store_true", help="decode workload only (profiling runs)")
@@ -806,6 +888,9 @@ def main():
         return
     if args.workload == "ragged":
         run_ragged(args)
+        return
+    if args.workload == "block":
+        run_block(args)
         return
     line, rank, world = run_decode(args)
     if rank == 0:

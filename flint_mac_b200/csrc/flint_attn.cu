@@ -97,7 +97,21 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
     // 512-key item (12.4 vs 10.3 us per launch for 32 sequences).  Full layers split down to 256 keys: there a lone
     // CTA scanning 1024 keys is slower than four CTAs and a merge (14.4 vs 11.1 us).
     const int min_chunk = is_swa ? 512 : 256;
-    const int chunk = round_up(int(std::max<long long>(min_chunk, (total + target_items - 1) / target_items)), 64);
+    int chunk = round_up(int(std::max<long long>(min_chunk, (total + target_items - 1) / target_items)), 64);
+    // Rounding every group to its nearest number of splits can overshoot the target (64 groups x 5 splits = 320 items
+    // for 296 slots: a second wave that nearly doubles the launch).  If it does, the chunk grows until the list fits.
+    auto count_items = [&](int c) {
+        long long items = 0;
+        for (int i = 0; i < n; i++) {
+            const int nk = hi[i] - lo[i];
+            int n_split = std::max(1, (nk + c / 2) / c);
+            const int per = std::max(64, round_up((nk + n_split - 1) / n_split, 64));
+            items += std::max(1, (nk + per - 1) / per);
+        }
+        return items * kNHeadKv;
+    };
+    for (int tries = 0; tries < 8 && chunk > min_chunk && count_items(chunk) > target_items && n * kNHeadKv <= target_items; tries++)
+        chunk = round_up(int((long long)chunk * count_items(chunk) / target_items) + 1, 64);
     n_groups = n * kNHeadKv;
     n_records = 0;
     n_subs = 0;

@@ -341,11 +341,20 @@ cudaError_t launch_proj(const ProjCall &c, ProjWorkspace &ws, int sm_count, cuda
     for (int b0 = 0; b0 < c.B; b0 += kProjMaxBatch) {
         const int bc = std::min(kProjMaxBatch, c.B - b0);
         const int nb = bc <= 8 ? 1 : bc <= 16 ? 2 : bc <= 32 ? 4 : 8;
-        // Split over K until there are about two CTAs per SM, in slices of at least 256 k; a full batch keeps slices
-        // of at least 1024 k so that the activation rows each CTA pulls from L2 stay below its weight bytes.
-        const int min_slice = nb == 8 ? 1024 : 256;
+        // Split over K so that the SMs carry equal loads: with s slices there are n_rb * s CTAs, the busiest SM runs
+        // ceil(n_rb * s / SMs) of them one after the other in effect (co-resident CTAs share the tensor pipe), each K / s
+        // long.  Slices of at least 256 k; a full batch keeps 512 so that the activation rows each CTA pulls from L2
+        // stay comparable to its weight bytes.
+        const int min_slice = nb == 8 ? 512 : 256;
         int n_split = 1;
-        while (n_rb * n_split < 2 * sm_count && c.K / (n_split * 2) >= min_slice && c.K % (n_split * 2 * kSub) == 0) n_split *= 2;
+        long long best = (long long)((n_rb + sm_count - 1) / sm_count) * c.K;
+        for (int s = 2; c.K / s >= min_slice && c.K % (s * kSub) == 0; s *= 2) {
+            const long long cost = (long long)((n_rb * s + sm_count - 1) / sm_count) * (c.K / s);
+            if (cost < best) {
+                best = cost;
+                n_split = s;
+            }
+        }
         const size_t need = n_split > 1 ? size_t(n_split) * nb * 8 * c.N : 0;
         if (need > ws.partial_floats) {
             if ((e = cudaDeviceSynchronize()) != cudaSuccess) return e;
