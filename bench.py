@@ -345,11 +345,12 @@ def decode_pass(torch, fa, h, local, world, n_loc, copies, args, hbm_peak, with_
     for i in range(args.warmup):
         step(i)
     barrier(world)
-    # On one GPU the kernel's own duration is taken inside the timed region (an event pair around every launch).  On
-    # several GPUs a step is a few tens of microseconds, and event records between the launches would be a visible
-    # part of it, so there the timed region runs bare and the same steps are repeated with the events afterwards.
-    timing_inside = world == 1
-    h.set_timing(timing_inside)
+    # The timed region runs bare: two events around all K steps.  A step is ONE launch of the decode kernel, so the
+    # region divided by the launches is that kernel's average duration in steady state (launch i+1 is scheduled while
+    # launch i still runs and waits, inside the kernel, for it to complete).  An event pair around every launch keeps
+    # the next launch from being scheduled early and reads several microseconds longer per launch; that figure is taken
+    # afterwards, over the same steps, and reported beside the first as kernel_us_isolated.
+    h.set_timing(False)
     launches0 = h.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     bytes_loc = 0
@@ -361,26 +362,27 @@ def decode_pass(torch, fa, h, local, world, n_loc, copies, args, hbm_peak, with_
         step(args.warmup + i)
     ev1.record()
     barrier(world)
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1), world)
+    ms_local = ev0.elapsed_time(ev1)
+    ms_total = max_over_ranks(ms_local, world)
     launches = h.launch_count() - launches0
-    if not timing_inside:
-        reset()
-        for i in range(args.warmup):
-            step(i)
-        torch.cuda.synchronize()
-        h.set_timing(True)
-        for i in range(args.steps):
-            step(args.warmup + i)
-        torch.cuda.synchronize()
+    reset()
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    h.set_timing(True)
+    for i in range(args.steps):
+        step(args.warmup + i)
+    torch.cuda.synchronize()
     kernel_ms, n_timed = h.kernel_ms()
     h.set_timing(False)
     bytes_loc /= args.steps                       # this rank's algorithmic bytes per step
     bytes_all = sum_over_ranks(bytes_loc, world)  # the job's
     ms_per_step = ms_total / args.steps
-    kernel_ms_avg = kernel_ms / max(n_timed, 1)
+    kernel_ms_avg = ms_local / max(launches, 1)   # this rank's launches over this rank's timed region
     res = {"ms_per_step": ms_per_step, "value": bytes_all / (ms_per_step * 1e-3) / 1e9, "bytes_per_step": bytes_all,
            "bytes_per_launch": bytes_loc, "kernel_us": kernel_ms_avg * 1e3,
-           "kernel_timed": "inside the timed region" if timing_inside else "same steps repeated with per-launch events",
+           "kernel_timed": "timed region / launches (one k_decode_attn launch per step, two events around the region)",
+           "kernel_us_isolated": kernel_ms / max(n_timed, 1) * 1e3,
            "achieved": bytes_loc / (kernel_ms_avg * 1e-3) / 1e9, "launches": launches,
            "n_seq_all": int(round(sum_over_ranks(n_loc, world)))}
     if with_e2e:
@@ -490,6 +492,7 @@ def run_decode(args):
                          "frac": strong["achieved"] / hbm_peak, "traffic": traffic, "traffic_source": traffic_source,
                          "peak_kind": f"of {peak_kind}", "kernel": "k_decode_attn (rank 0's launch)",
                          "kernel_us": strong["kernel_us"], "kernel_timed": strong["kernel_timed"],
+                         "kernel_us_isolated": strong["kernel_us_isolated"],
                          "bytes_per_launch": strong["bytes_per_launch"]},
             "e2e": {"value": strong["e2e_value"], "unit": "GB/s", "ms_per_step": strong["e2e_ms"],
                     "h2d_bytes_per_step": n_loc * QKV_DIM * 2, "d2h_bytes_per_step": n_loc * OUT_DIM * 2,
@@ -682,7 +685,6 @@ def run_longctx(args):
     for i in range(args.warmup):
         step(i)
     barrier(world)
-    h.set_timing(True)
     launches0 = h.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
@@ -692,11 +694,21 @@ def run_longctx(args):
         ev1.record()
         barrier(world)
     ms = max_over_ranks(ev0.elapsed_time(ev1), world) / args.steps
+    launches = h.launch_count() - launches0
+    # the decode kernel alone: the same steps once more with an event pair around every launch of it (inside the timed
+    # region those events would keep the next launch from being scheduled early and cost microseconds per step)
+    barrier(world)
+    h.set_timing(True)
+    for i in range(args.steps):
+        step(args.warmup + i)
+    torch.cuda.synchronize()
     kernel_ms, n_timed = h.kernel_ms()
     h.set_timing(False)
-    launches = h.launch_count() - launches0
+    barrier(world)
     step_bytes = decode_bytes(1, S)
-    kernel_us = kernel_ms / max(n_timed, 1) * 1e3
+    kernel_us_isolated = kernel_ms / max(n_timed, 1) * 1e3
+    # one GPU: the step IS one launch of the decode kernel, so the bare region gives its steady-state duration
+    kernel_us = ms * 1e3 if world == 1 else kernel_us_isolated
     h.check()
     h.close()
     if rank == 0:
@@ -717,7 +729,9 @@ def run_longctx(args):
                              "frac": per_gpu / (kernel_us * 1e-6) / 1e9 / hbm_peak, "traffic": None,
                              "peak_kind": f"of {peak_kind}", "kernel": "k_decode_attn (this rank's key range)",
                              "kernel_us": kernel_us, "bytes_per_launch": per_gpu},
-                "merge_us": ms * 1e3 - kernel_us, "gpu_launches": launches, "clocks": clk.summary()}
+                "kernel_timed": "timed region / launches (one launch per step)" if world == 1 else
+                                "same steps repeated with an event pair around every k_decode_attn launch",
+                "kernel_us_isolated": kernel_us_isolated, "step_minus_kernel_us": ms * 1e3 - kernel_us, "gpu_launches": launches, "clocks": clk.summary()}
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

@@ -77,6 +77,11 @@ struct DecParams {
     const int32_t *block_table;
     int table_stride;
     int paged;
+    // Full layers of a handle: K/V tiles arrive by TMA.  k_map / v_map point at CUtensorMap objects in device memory
+    // that describe the layer's cache (or page pool) as rows of 128 halves, {128, rows}, box {64, 64}, 128-byte
+    // swizzle; null: tiles are fetched with 16-byte cp.async (ring layers, caller-owned caches).
+    const void *k_map, *v_map;
+    int *error_flag;  // set when a bounded wait of the TMA variant runs out (null: not reported)
 };
 constexpr int kPageKeys = 64;                   // keys per KV page = one decode tile
 

@@ -36,10 +36,11 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 template <int kStages>
-struct __align__(16) DecSmem {
+struct __align__(1024) DecSmem {
     unsigned char k[kStages][kTileBytes];
     unsigned char v[kStages][kTileBytes];
-    __half q[kGqa][kHeadDim];   // normalised, rotated, pre-scaled query heads of the group
+    alignas(16) unsigned long long full_bar[kStages];  // TMA variant: the K and V tile of the stage have landed
+    alignas(16) __half q[kGqa][kHeadDim];   // normalised, rotated, pre-scaled query heads of the group
     __half knew[kHeadDim];      // the new token's K (after norm/RoPE) and V as stored in the cache
     __half vnew[kHeadDim];
     float red_m[kWarps][kGqa];
@@ -50,7 +51,64 @@ struct __align__(16) DecSmem {
 };
 // The per-warp output accumulators are merged through the (by then idle) K tiles.
 static_assert(sizeof(float) * kWarps * kGqa * kHeadDim <= kStagesWave * kTileBytes, "merge buffer aliases the K tiles");
-static_assert(sizeof(DecSmem<kStagesDeep>) <= 227 * 1024, "one CTA per SM");
+static_assert(sizeof(DecSmem<kStagesDeep>) + 1024 <= 227 * 1024, "one CTA per SM");
+
+// Byte offset of 16-byte chunk `ch` (0..15) of row `row` inside a 64-row K or V tile in shared memory.
+//  cp.async layout: rows of 256 bytes, chunk index XOR (row % 8): conflict-free for ldmatrix.
+//  TMA layout: two halves of [64 rows][128 bytes] (dims 0-63, dims 64-127), each with the hardware's 128-byte swizzle,
+//  which is the same XOR applied to the chunk index within the 128-byte row (tile bases are 1024-byte aligned).
+template <bool kTma>
+__device__ __forceinline__ uint32_t tile_off(int row, int ch) {
+    if (kTma) return uint32_t((ch >> 3) * (kTileBytes / 2) + row * 128 + (((ch & 7) ^ (row & 7)) << 4));
+    return uint32_t(row * kRowBytes + ((ch ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.b32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded: gives up after ~2^28 SM cycles, far beyond anything a healthy launch needs.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > (1ll << 28)) return false;
+    }
+}
+// One 64-column x 64-row box of a {128, rows} half tensor into shared memory (no multicast).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// sin and cos of a float angle of any size.  The angle is brought into [-pi, pi] in double first (exact to ~1e-11 for
+// the 1e5-radian angles of a 131072-token context), which keeps sincosf off its long-argument path: that path alone
+// cost the CTAs of such a context about two microseconds before their first tile could be used.
+__device__ __forceinline__ void sincos_reduced(float x, float *sn, float *cs) {
+    const double xd = double(x);
+    const double k = rint(xd * 0.15915494309189535);
+    double r = fma(-k, 6.283185307179586, xd);
+    r = fma(-k, 2.4492935982947064e-16, r);
+    sincosf(float(r), sn, cs);
+}
 
 __device__ __forceinline__ float4 load_row4(const void *base, int dtype, size_t elem0, int lane) {
     if (dtype == kDtypeF32) return reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem0)[lane];
@@ -185,10 +243,12 @@ __device__ __forceinline__ Merged merge_records(const float *rec, int n, int d0,
     return r;
 }
 
-template <int kStages>
+template <int kStages, bool kTma>
 __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &it) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    DecSmem<kStages> &sm = *reinterpret_cast<DecSmem<kStages> *>(smem_raw);
+    // swizzled TMA tiles need 1024-byte alignment: the launch asks for 1 KiB more than the struct and rounds up here
+    DecSmem<kStages> &sm = *reinterpret_cast<DecSmem<kStages> *>(
+        smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t4 = lane & 3;
@@ -208,6 +268,24 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     auto load_tile = [&](int t) {
         const int stage = t % kStages;
         const int jt = j0 + t * kTileKeys;
+        if (kTma) {
+            // One thread asks for the whole tile: two 64-dim halves of K and of V, 32 KiB on one barrier.  Rows past
+            // the item's range are real cache rows (later keys, or slots never written): they are masked below, and
+            // the caches of a handle only ever hold finite values.
+            if (tid == 0) {
+                int y;
+                if (p.paged) y = (p.block_table[size_t(it.seq) * p.table_stride + (jt >> 6)] * kNHeadKv + it.kvh) * kPageKeys;
+                else y = (it.seq * kNHeadKv + it.kvh) * p.n_slots + (jt - p.kv_lo);
+                const uint32_t bar = smem_u32(&sm.full_bar[stage]);
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // earlier generic accesses to the stage
+                mbar_expect_tx(bar, 2 * kTileBytes);
+                tma_load_2d(ks_addr + stage * kTileBytes, p.k_map, bar, 0, y);
+                tma_load_2d(ks_addr + stage * kTileBytes + kTileBytes / 2, p.k_map, bar, 64, y);
+                tma_load_2d(vs_addr + stage * kTileBytes, p.v_map, bar, 0, y);
+                tma_load_2d(vs_addr + stage * kTileBytes + kTileBytes / 2, p.v_map, bar, 64, y);
+            }
+            return;
+        }
         // paged layer: this tile is one page (jt is a multiple of 64); its rows are slots 0..63 of the page
         const __half *kb = kbase, *vb = vbase;
         if (p.paged) {
@@ -224,7 +302,7 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
             const bool valid = j < j1;  // cached keys only; other rows are zero-filled
             const int slot = !valid ? 0 : p.paged ? row : int(uint32_t(j) & p.slot_mask) - p.kv_lo;
             const size_t off = size_t(slot) * kHeadDim + ch * 8;
-            const uint32_t dst = stage * kTileBytes + row * kRowBytes + ((ch ^ (row & 7)) << 4);
+            const uint32_t dst = stage * kTileBytes + tile_off<false>(row, ch);
             cp_async16(ks_addr + dst, kb + off, valid ? 16u : 0u);
             cp_async16(vs_addr + dst, vb + off, valid ? 16u : 0u);
         }
@@ -248,6 +326,11 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     // contents, split-K scratch and counters) is read or written before this wait, which returns once every
     // earlier kernel of the stream has completed and its writes are visible.
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    if (kTma && tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; s++) mbar_init(smem_u32(&sm.full_bar[s]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
     float4 q[2];
 #pragma unroll
     for (int i = 0; i < 2; i++)
@@ -266,7 +349,7 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         const float qscale = rsqrtf(float(kHeadDim)) * kLog2e;  // softmax runs in base 2
         if (rope && tid < kHeadDim / 2) {
             float sn, cs;
-            sincosf(float(it.pos) * freq, &sn, &cs);
+            sincos_reduced(float(it.pos) * freq, &sn, &cs);
             sm.rope_cos[tid] = cs;
             sm.rope_sin[tid] = sn;
         }
@@ -316,10 +399,20 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     const int new_row = it.fold ? (it.pos - j0) % kTileKeys : -1;
 
     for (int t = 0; t < n_tiles; t++) {
-        cp_async_wait<kStages - 2>();
-        __syncthreads();
+        if (kTma) {
+            // every thread waits for the tile itself (bounded); if any wait ran out, the whole CTA reports it and
+            // leaves together (the barrier below carries the decision)
+            const bool late = !mbar_wait_bounded(smem_u32(&sm.full_bar[t % kStages]), uint32_t(t / kStages) & 1u);
+            if (__syncthreads_or(late)) {
+                if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 4);
+                return;
+            }
+        } else {
+            cp_async_wait<kStages - 2>();
+            __syncthreads();
+        }
         if (t + kStages - 1 < n_tiles) load_tile(t + kStages - 1);
-        cp_async_commit();
+        if (!kTma) cp_async_commit();
 
         const int stage = t % kStages;
         const int jw = j0 + t * kTileKeys + 16 * warp;  // first key of this warp's 16-row slice
@@ -331,18 +424,19 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
                                         : reinterpret_cast<const uint4 *>(sm.vnew)[lane - 16];
             unsigned char *tile = lane < 16 ? sm.k[stage] : sm.v[stage];
             const int ch = lane & 15;
-            *reinterpret_cast<uint4 *>(tile + new_row * kRowBytes + ((ch ^ (new_row & 7)) << 4)) = val;
+            *reinterpret_cast<uint4 *>(tile + tile_off<kTma>(new_row, ch)) = val;
             __syncwarp();
         }
 
         // S^T (16 keys x 8 heads) = K . Q^T
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         {
-            const uint32_t base = ks_addr + stage * kTileBytes + (16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8) * kRowBytes;
+            const uint32_t base = ks_addr + stage * kTileBytes;
+            const int row = 16 * warp + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
             for (int k = 0; k < 8; k++) {
                 uint32_t a[4];
-                ldmatrix_x4(a, base + (((2 * k + (lane >> 4)) ^ (lane & 7)) << 4));
+                ldmatrix_x4(a, base + tile_off<kTma>(row, 2 * k + (lane >> 4)));
                 mma_16816(s, a, bq[k][0], bq[k][1]);
             }
         }
@@ -370,17 +464,18 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
 
         // O^T (128 dims x 8 heads) = O^T * corr + V^T . P^T
         {
-            const uint32_t base = vs_addr + stage * kTileBytes + (16 * warp + (lane & 7) + (lane >> 4) * 8) * kRowBytes;
+            const uint32_t base = vs_addr + stage * kTileBytes;
+            const int row = 16 * warp + (lane & 7) + (lane >> 4) * 8;
 #pragma unroll
             for (int dm = 0; dm < 8; dm++) {
                 uint32_t a[4];
-                ldmatrix_x4_trans(a, base + (((2 * dm + ((lane >> 3) & 1)) ^ (lane & 7)) << 4));
+                ldmatrix_x4_trans(a, base + tile_off<kTma>(row, 2 * dm + ((lane >> 3) & 1)));
                 o[dm][0] *= c0; o[dm][1] *= c1; o[dm][2] *= c0; o[dm][3] *= c1;
                 mma_16816(o[dm], a, b0, b1);
             }
         }
     }
-    cp_async_wait<0>();
+    if (!kTma) cp_async_wait<0>();
     __syncthreads();  // every warp is done with the tiles: the K tiles become the merge buffer
 
     // ---- merge the four warps --------------------------------------------------------------------------------
@@ -528,16 +623,22 @@ struct DecItemsParam {
     DecItem items[kCap];
 };
 
+template <bool kTma>
 __global__ void __launch_bounds__(kThreads, 2) k_decode_attn(const DecParams p) {
     const DecItem it = p.items[blockIdx.x];
-    decode_item<kStagesWave>(p, it);
+    decode_item<kStagesWave, kTma>(p, it);
 }
 
-template <int kCap, int kStages>
+template <int kCap, int kStages, bool kTma>
 __global__ void __launch_bounds__(kThreads, kStages == kStagesWave ? 2 : 1)
     k_decode_attn_p(const __grid_constant__ DecParams p, const __grid_constant__ DecItemsParam<kCap> ip) {
     const DecItem it = ip.items[blockIdx.x];
-    decode_item<kStages>(p, it);
+    decode_item<kStages, kTma>(p, it);
+}
+
+template <int kStages>
+constexpr size_t smem_bytes() {  // 1 KiB of slack for the 1024-byte alignment of the tiles
+    return sizeof(DecSmem<kStages>) + 1024;
 }
 
 constexpr int kCapSmall = 76, kCapMid = 256;
@@ -571,7 +672,8 @@ template <int kCap, int kStages>
 cudaError_t launch_inline(const DecParams &p, const DecItem *host_items, int n_items, cudaStream_t stream) {
     static thread_local DecItemsParam<kCap> ip;  // copied into the launch by the runtime before this returns
     memcpy(ip.items, host_items, sizeof(DecItem) * size_t(n_items));
-    return launch_pdl(k_decode_attn_p<kCap, kStages>, n_items, sizeof(DecSmem<kStages>), stream, p, ip);
+    if (p.k_map) return launch_pdl(k_decode_attn_p<kCap, kStages, true>, n_items, smem_bytes<kStages>(), stream, p, ip);
+    return launch_pdl(k_decode_attn_p<kCap, kStages, false>, n_items, smem_bytes<kStages>(), stream, p, ip);
 }
 
 template <typename K>
@@ -624,19 +726,26 @@ __global__ void __launch_bounds__(kHeadDim) k_combine_parts(const CombineParams 
 }  // namespace
 
 cudaError_t decode_kernel_setup() {
-    constexpr size_t wave = sizeof(DecSmem<kStagesWave>), deep = sizeof(DecSmem<kStagesDeep>);
-    cudaError_t e = allow_smem(k_decode_attn, wave);
-    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesWave>, wave);
-    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesWave>, wave);
-    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kMaxParamItems, kStagesWave>, wave);
-    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesDeep>, deep);
-    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesDeep>, deep);
+    constexpr size_t wave = smem_bytes<kStagesWave>(), deep = smem_bytes<kStagesDeep>();
+    cudaError_t e = allow_smem(k_decode_attn<false>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn<true>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesWave, false>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesWave, false>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kMaxParamItems, kStagesWave, false>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesDeep, false>, deep);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesDeep, false>, deep);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesWave, true>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesWave, true>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kMaxParamItems, kStagesWave, true>, wave);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapSmall, kStagesDeep, true>, deep);
+    if (e == cudaSuccess) e = allow_smem(k_decode_attn_p<kCapMid, kStagesDeep, true>, deep);
     return e;
 }
 
 cudaError_t launch_decode(const DecParams &p, int n_items, cudaStream_t stream) {
     if (n_items <= 0) return cudaSuccess;
-    return launch_pdl(k_decode_attn, n_items, sizeof(DecSmem<kStagesWave>), stream, p);
+    if (p.k_map) return launch_pdl(k_decode_attn<true>, n_items, smem_bytes<kStagesWave>(), stream, p);
+    return launch_pdl(k_decode_attn<false>, n_items, smem_bytes<kStagesWave>(), stream, p);
 }
 
 cudaError_t launch_decode_inline(const DecParams &p, const DecItem *host_items, int n_items, int sm_count,

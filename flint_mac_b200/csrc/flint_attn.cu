@@ -43,6 +43,7 @@ struct Layer {
     float *q_norm = nullptr, *k_norm = nullptr, *sinks = nullptr;  // device copies
     // projections either side of attention (optional): attn_norm [n_embd] fp32, W_qkv [5120][n_embd] bf16 (q rows,
     // then k rows, then v rows: the packed row of src/metal/fused.metal:211), W_o [n_embd][4096] bf16
+    unsigned char *kv_maps = nullptr;  // full layers: two tensor maps (K, V) in device memory for the decode kernel's TMA loads
     int n_embd = 0;
     float *attn_norm = nullptr;
     __nv_bfloat16 *w_qkv = nullptr, *w_o = nullptr;
@@ -203,6 +204,7 @@ struct flint_attn {
     std::vector<int32_t> seq_blocks;   // blocks each sequence holds
     std::vector<int32_t> free_pages;   // stack of free page numbers
     int32_t *table_dev = nullptr;
+    int *dec_err = nullptr;  // device word the decode kernel sets when a bounded wait runs out
     std::vector<Layer> layers;
     std::vector<int32_t> pos;
     float *inv_freq = nullptr;
@@ -247,8 +249,9 @@ struct flint_attn {
         cudaSetDevice(device);
         for (auto &L : layers) {
             cudaFree(L.k); cudaFree(L.v); cudaFree(L.q_norm); cudaFree(L.k_norm); cudaFree(L.sinks);
-            cudaFree(L.attn_norm); cudaFree(L.w_qkv); cudaFree(L.w_o);
+            cudaFree(L.attn_norm); cudaFree(L.w_qkv); cudaFree(L.w_o); cudaFree(L.kv_maps);
         }
+        cudaFree(dec_err);
         proj_workspace_free(proj_ws);
         cudaFree(block_buf);
         cudaFree(table_dev);
@@ -467,6 +470,9 @@ struct flint_attn {
         dp.paged = L.paged ? 1 : 0;
         dp.block_table = table_dev;
         dp.table_stride = pages_per_seq;
+        dp.k_map = L.kv_maps;
+        dp.v_map = L.kv_maps ? L.kv_maps + 128 : nullptr;
+        dp.error_flag = dec_err;
         if (mode == 2) {
             const size_t rec_bytes = size_t(xchg_n) * kNHead * kPartialDim * sizeof(float);
             const size_t buf_off = 256 + size_t(step & 1) * kv_ranks * rec_bytes + size_t(kv_rank) * rec_bytes;
@@ -542,6 +548,8 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
         for (int i = 0; i < kRing; i++) CK(cudaEventCreateWithFlags(&a->ring_ev[i], cudaEventDisableTiming));
         CK(decode_kernel_setup());
         CK(prefill_kernel_setup());
+        CK(cudaMalloc(&a->dec_err, sizeof(int)));
+        CK(cudaMemset(a->dec_err, 0, sizeof(int)));
         float freq[kHeadDim / 2];
         for (int i = 0; i < kHeadDim / 2; i++) freq[i] = powf(kRopeTheta, -2.0f * i / kHeadDim);  // ref_model.cpp:55
         CK(cudaMalloc(&a->inv_freq, sizeof(freq)));
@@ -570,6 +578,22 @@ flint_attn *flint_attn_open(const flint_attn_config *cfg, char *err, int32_t err
             CK(cudaMalloc(&L.v, bytes));
             CK(cudaMemset(L.k, 0, bytes));
             CK(cudaMemset(L.v, 0, bytes));
+            // Full layers feed the decode kernel's K/V tiles by TMA (FLINT_ATTN_NO_TMA=1 keeps the cp.async path).
+            static const bool no_tma = [] {
+                const char *v = getenv("FLINT_ATTN_NO_TMA");
+                return v && v[0] == '1';
+            }();
+            if (!L.is_swa && !no_tma) {
+                const long long rows = L.paged ? (long long)cfg->kv_pages * kNHeadKv * kPageKeys
+                                               : (long long)cfg->max_seqs * kNHeadKv * L.n_slots;
+                if (rows < (1ll << 31)) {  // TMA coordinates are 32-bit
+                    alignas(64) unsigned char maps[256];
+                    CK(make_kv_rows_map(maps, L.k, rows));
+                    CK(make_kv_rows_map(maps + 128, L.v, rows));
+                    CK(cudaMalloc(&L.kv_maps, sizeof(maps)));
+                    CK(cudaMemcpy(L.kv_maps, maps, sizeof(maps), cudaMemcpyHostToDevice));
+                }
+            }
             CK(cudaMalloc(&L.q_norm, kHeadDim * sizeof(float)));
             CK(cudaMalloc(&L.k_norm, kHeadDim * sizeof(float)));
             CK(cudaMalloc(&L.sinks, kNHead * sizeof(float)));
@@ -1017,6 +1041,11 @@ int32_t flint_attn_check(flint_attn *a, char *err, int32_t err_len) {
     int flag = 0;
     CK(prefill_error_flag(a->pf, &flag));
     if (flag) throw std::runtime_error("prefill kernel reported device error " + std::to_string(flag));
+    CK(cudaMemcpy(&flag, a->dec_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag) {
+        CK(cudaMemset(a->dec_err, 0, sizeof(int)));
+        throw std::runtime_error("decode kernel reported device error " + std::to_string(flag));
+    }
     if (a->xchg) {
         int *word = reinterpret_cast<int *>(a->xchg + kMaxPeers * sizeof(uint32_t));
         CK(cudaMemcpy(&flag, word, sizeof(int), cudaMemcpyDeviceToHost));

@@ -977,6 +977,19 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     return cudaSuccess;
 }
 
+cudaError_t make_kv_rows_map(void *map_out, const void *base, long long n_rows) {
+    if (!g_encode) return cudaErrorNotSupported;
+    const cuuint64_t dims[2] = {cuuint64_t(kHeadDim), cuuint64_t(n_rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(kHeadDim) * 2};
+    const cuuint32_t box[2] = {64, 64};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(static_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                                const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 cudaError_t launch_prefill_combine(const float *parts_o, const float *parts_ml, int n_parts, int n_tok, void *out,
                                    int out_dtype, cudaStream_t stream) {
     if (n_tok <= 0 || n_parts <= 0) return cudaSuccess;

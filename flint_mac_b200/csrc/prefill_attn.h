@@ -42,6 +42,9 @@ struct PrefillWorkspace {
 };
 
 cudaError_t prefill_kernel_setup();
+// A tensor map (128 bytes, written to map_out on the host) over a K or V cache seen as n_rows rows of 128 halves:
+// {128, n_rows}, box {64 halves, 64 rows}, 128-byte swizzle -- what the decode kernel's TMA tile loads use.
+cudaError_t make_kv_rows_map(void *map_out, const void *base, long long n_rows);
 cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStream_t stream, int *n_launches);
 void prefill_workspace_free(PrefillWorkspace &ws);
 // parts_o [n_parts][n_tok][4096] fp32, parts_ml [n_parts][n_tok][32][2] -> out [n_tok][4096]: log-sum-exp merge of the
