@@ -265,22 +265,26 @@ def measure_prefill(torch, fa, local, iters: int, warmup: int, T: int = PREFILL_
     out = torch.empty(T, OUT_DIM, device="cuda", dtype=torch.bfloat16)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
+    # Two passes over the same work.  The first runs bare, an event pair around the whole prefill: the step as a
+    # caller sees it (the attention kernel is scheduled while the prologue drains).  The second has the library put an
+    # event pair around the attention kernel, which gives that kernel's own duration but keeps it from starting early.
     step_ms = []
-    h.set_timing(True)
-    for i in range(warmup + iters):
-        h.set_pos(0, history)
-        flush.fill_(i & 0xFF)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if i == warmup:
-            torch.cuda.synchronize()
-            h.kernel_ms()  # drop the warm-up records
-            launches0 = h.launch_count()
-        e0.record()
-        h.prefill_dev(0, 0, T, qkv, fa.BF16, out, fa.BF16, stream)
-        e1.record()
-        if i >= warmup:
-            step_ms.append((e0, e1))
-    torch.cuda.synchronize()
+    for timing in (False, True):
+        h.set_timing(timing)
+        for i in range(warmup + iters):
+            h.set_pos(0, history)
+            flush.fill_(i & 0xFF)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if i == warmup:
+                torch.cuda.synchronize()
+                h.kernel_ms()  # drop the warm-up records
+                launches0 = h.launch_count()
+            e0.record()
+            h.prefill_dev(0, 0, T, qkv, fa.BF16, out, fa.BF16, stream)
+            e1.record()
+            if i >= warmup and not timing:
+                step_ms.append((e0, e1))
+        torch.cuda.synchronize()
     attn_ms, n = h.kernel_ms()
     launches_per_step = (h.launch_count() - launches0) // max(iters, 1)
     h.set_timing(False)

@@ -843,6 +843,7 @@ static void prefill_impl(flint_attn *a, int layer, int seq, int n_tok, const voi
     if ((qkv_dtype != kDtypeF32 && qkv_dtype != kDtypeBf16) ||
         (!partial_o && out_dtype != kDtypeF32 && out_dtype != kDtypeBf16))
         throw std::runtime_error("bad dtype");
+    if (reinterpret_cast<uintptr_t>(qkv) & 15) throw std::runtime_error("q/k/v rows must start on a 16-byte boundary");
     PrefillParams pp{};
     pp.qkv = qkv; pp.out = out;
     pp.qkv_dtype = qkv_dtype; pp.out_dtype = out_dtype;

@@ -95,108 +95,174 @@ struct PrologueArgs {
     __half *k_st, *v_st;        // [4][n_hist + n_tok][128] (ring layers only; null otherwise)
     int n_slots, is_swa, has_rope, qkv_dtype;
     int p0, n_tok, n_hist;
-    int history_pass;  // 1: only copy the history rows out of the ring; 0: only the new tokens
     const int32_t *block_table;  // paged full layer: k_cache / v_cache are page pools, slot = page * 64 + pos % 64
     int kv_lo, kv_hi;            // full layer: positions this device's cache holds (slot = pos - kv_lo); others are not stored
 };
 
-__device__ __forceinline__ float4 pf_load_row4(const void *base, int dtype, size_t elem0, int lane) {
-    if (dtype == kDtypeF32) return reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem0)[lane];
-    const uint2 u = reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + elem0)[lane];
-    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(&u.x);
-    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162 *>(&u.y);
-    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+// A lane's share of an input row of 128: dims 4*sub..4*sub+3 and the four 64 further on, the partners of the first
+// four under NEOX RoPE, so that the rotation needs no exchange between lanes.  Two 8-byte loads for bf16 rows, two
+// 16-byte loads for fp32 rows; they stay packed in registers until the row is worked on, so that a warp has all its
+// loads in flight first.
+template <bool kBf16>
+struct ProRaw;
+template <>
+struct ProRaw<true> {
+    uint2 lo, hi;
+    __device__ __forceinline__ void load(const void *base, size_t elem) {
+        lo = *reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + elem);
+        hi = *reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + elem + kHeadDim / 2);
+    }
+    __device__ __forceinline__ void unpack(float (&x)[8]) const {
+        const uint32_t w[4] = {lo.x, lo.y, hi.x, hi.y};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            x[2 * i] = __uint_as_float(w[i] << 16);
+            x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+template <>
+struct ProRaw<false> {
+    float4 lo, hi;
+    __device__ __forceinline__ void load(const void *base, size_t elem) {
+        lo = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem);
+        hi = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem + kHeadDim / 2);
+    }
+    __device__ __forceinline__ void unpack(float (&x)[8]) const {
+        x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w; x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    }
+};
+
+// x[0..3] -> dst[0..3], x[4..7] -> dst[64..67], as halves
+__device__ __forceinline__ void pf_store_half44(__half *dst, const float (&v)[8]) {
+    *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+    *reinterpret_cast<uint2 *>(dst + kHeadDim / 2) = make_uint2(pack_half2(v[4], v[5]), pack_half2(v[6], v[7]));
 }
 
-// RMSNorm with weight, then NEOX RoPE with this token's (cos, sin) per owned dim; lane owns dims 4*lane..4*lane+3 and
-// pairs with lane^16 (same arithmetic as src/ref/ref_model.cpp:45-61).
-__device__ __forceinline__ float4 pf_norm_rope(float4 v, const float4 wv, const float (&cs)[4], const float (&sn)[4],
-                                               int lane, bool rope) {
-    const float ss = warp_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w);
-    const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps);
-    float x[4] = {v.x * scale * wv.x, v.y * scale * wv.y, v.z * scale * wv.z, v.w * scale * wv.w};
+// RMSNorm with weight, then NEOX RoPE with this token's (cos, sin) per owned pair of dims (same arithmetic as
+// src/ref/ref_model.cpp:45-61; `extra` is 1 for keys).  A row of 128 lives in 16 lanes; the two halves of a warp hold
+// two different rows.  x[j] and x[j + 4] are dims d and d + 64.
+__device__ __forceinline__ void pf_norm_rope8(float (&x)[8], const float (&w)[8], const float (&cs)[4],
+                                              const float (&sn)[4], bool rope, float extra) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+#pragma unroll
+    for (int off = 1; off < 16; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps) * extra;
+#pragma unroll
+    for (int j = 0; j < 8; j++) x[j] = x[j] * scale * w[j];
     if (rope) {
-        float out[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float partner = __shfl_xor_sync(0xffffffffu, x[j], 16);
-            out[j] = lane < 16 ? x[j] * cs[j] - partner * sn[j] : partner * sn[j] + x[j] * cs[j];
+            const float lo = x[j], hi = x[j + 4];
+            x[j] = lo * cs[j] - hi * sn[j];
+            x[j + 4] = lo * sn[j] + hi * cs[j];
         }
-#pragma unroll
-        for (int j = 0; j < 4; j++) x[j] = out[j];
     }
-    return make_float4(x[0], x[1], x[2], x[3]);
 }
 
-__device__ __forceinline__ void pf_store_half4(__half *dst, float4 v) {
-    *reinterpret_cast<uint2 *>(dst) = make_uint2(pack_half2(v.x, v.y), pack_half2(v.z, v.w));
-}
+constexpr int kProRows = 10;  // input rows (heads) per warp: a token's 40 rows (32 q, 4 k, 4 v) take the four warps of a CTA
 
-// New-token pass: one warp per (token, group of 8 head rows): groups 0-3 are the 32 q heads, group 4 the 4 k and
-// 4 v heads.  The 8 rows are loaded up front (8 independent loads per lane) and the token's cos/sin are computed
-// once per warp, not once per head.  History pass (ring layers with p0 > 0): one warp per (history row, kv head)
-// copies the up to 512 keys before p0 out of the ring into the linear staging the attention kernel reads.  The
-// history pass is its own, earlier launch: tokens p0+512.. of a long prompt land in the very ring slots the history
-// occupies (which is why the reference prefills in chunks of at most 512, src/metal/flint_config.h:29-31).
-__global__ void __launch_bounds__(256) k_prefill_prologue(const PrologueArgs a) {
+// New-token pass: one CTA of four warps per token, each warp with ten of its 40 head rows, two rows per pass (one per
+// half-warp).  All loads of a warp go out before the first row is touched.  The token's 64 (cos, sin) pairs are
+// evaluated once, by the first warp, and shared through shared memory.
+template <bool kBf16>
+__device__ __forceinline__ void prologue_rows(const PrologueArgs &a) {
+    __shared__ float2 s_cs[kHeadDim / 2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row = (long long)blockIdx.x * 8 + warp;
-    if (a.history_pass) {
-        if (row >= (long long)a.n_hist * kNHeadKv) return;
-        const int r = int(row / kNHeadKv), kvh = int(row % kNHeadKv);
-        const int pos = a.p0 - a.n_hist + r, slot = pos & (kSwaRing - 1);
-        const size_t src = (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane;
-        const size_t dst = (size_t(kvh) * (a.n_hist + a.n_tok) + r) * kHeadDim + 4 * lane;
-        *reinterpret_cast<uint2 *>(a.k_st + dst) = *reinterpret_cast<const uint2 *>(a.k_cache + src);
-        *reinterpret_cast<uint2 *>(a.v_st + dst) = *reinterpret_cast<const uint2 *>(a.v_cache + src);
-        return;
-    }
-    if (row >= (long long)a.n_tok * 5) return;
-    const int t = int(row / 5), grp = int(row % 5), pos = a.p0 + t;
-    const size_t in0 = size_t(t) * kQkvDim + size_t(grp) * 8 * kHeadDim;  // group 4 starts at 4096: k heads then v heads
-    float4 x[8];
+    const int t = blockIdx.x, pos = a.p0 + t, half = lane >> 4, sub = lane & 15;
+    const bool rope = a.has_rope != 0;
+    const size_t in0 = size_t(t) * kQkvDim + size_t(warp * kProRows + half) * kHeadDim + 4 * sub;
+
+    ProRaw<kBf16> raw[kProRows / 2];
 #pragma unroll
-    for (int i = 0; i < 8; i++) x[i] = pf_load_row4(a.qkv, a.qkv_dtype, in0 + size_t(i) * kHeadDim, lane);
-    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
-    if (a.has_rope) {
-        const float4 fr = reinterpret_cast<const float4 *>(a.inv_freq)[lane & 15];
-        const float freq[4] = {fr.x, fr.y, fr.z, fr.w};
-#pragma unroll
-        for (int j = 0; j < 4; j++) sincosf(float(pos) * freq[j], &sn[j], &cs[j]);
+    for (int i = 0; i < kProRows / 2; i++) raw[i].load(a.qkv, in0 + size_t(2 * i) * kHeadDim);
+
+    if (rope && warp == 0) {
+        const float2 fr = reinterpret_cast<const float2 *>(a.inv_freq)[lane];
+        float s0, c0, s1, c1;
+        sincosf(float(pos) * fr.x, &s0, &c0);
+        sincosf(float(pos) * fr.y, &s1, &c1);
+        *reinterpret_cast<float4 *>(&s_cs[2 * lane]) = make_float4(c0, s0, c1, s1);
     }
-    if (grp < 4) {
-        const float4 wv = reinterpret_cast<const float4 *>(a.q_norm)[lane];
-        const float sc = rsqrtf(float(kHeadDim)) * kLog2e;
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float4 q = pf_norm_rope(x[i], wv, cs, sn, lane, a.has_rope != 0);
-            q.x *= sc; q.y *= sc; q.z *= sc; q.w *= sc;
-            pf_store_half4(a.q_st + (size_t(grp * 8 + i) * a.n_tok + t) * kHeadDim + 4 * lane, q);
-        }
-        return;
+    float wq[8];
+    {
+        const float4 q0 = __ldg(reinterpret_cast<const float4 *>(a.q_norm) + sub);
+        const float4 q1 = __ldg(reinterpret_cast<const float4 *>(a.q_norm) + 16 + sub);
+        wq[0] = q0.x; wq[1] = q0.y; wq[2] = q0.z; wq[3] = q0.w; wq[4] = q1.x; wq[5] = q1.y; wq[6] = q1.z; wq[7] = q1.w;
     }
-    const float4 wk = reinterpret_cast<const float4 *>(a.k_norm)[lane];
+    const float sc = rsqrtf(float(kHeadDim)) * kLog2e;
     const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos - a.kv_lo;  // prefill.metal:106
     const bool mine = a.is_swa || (pos >= a.kv_lo && pos < a.kv_hi);
+    // On a ring layer tokens t and t + 1024 of one launch share a slot: only the last token that maps to a slot
+    // stores there, so the ring's final contents do not depend on the order in which the CTAs run.
+    const bool to_cache = mine && (!a.is_swa || t + kSwaRing >= a.n_tok);
     // paged layer: [page][kv head][64 slots][128] instead of [kv head][slot][128]
     const size_t page = a.block_table ? size_t(a.block_table[pos >> 6]) : 0;
+    __syncthreads();
+    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (rope) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const bool is_k = i < kNHeadKv;
-        const int kvh = i & (kNHeadKv - 1);
-        const float4 y = is_k ? pf_norm_rope(x[i], wk, cs, sn, lane, a.has_rope != 0) : x[i];
-        // On a ring layer tokens t and t + 1024 of one launch share a slot: only the last token that maps to a slot
-        // stores there, so the ring's final contents do not depend on the order in which the CTAs run.
-        if (mine && (!a.is_swa || t + kSwaRing >= a.n_tok)) {
+        for (int j = 0; j < 4; j += 2) {
+            const float4 v = *reinterpret_cast<const float4 *>(&s_cs[4 * sub + j]);
+            cs[j] = v.x; sn[j] = v.y; cs[j + 1] = v.z; sn[j + 1] = v.w;
+        }
+    }
+
+#pragma unroll
+    for (int i = 0; i < kProRows / 2; i++) {
+        const int row = warp * kProRows + 2 * i + half;  // 0-31 q heads, 32-35 k heads, 36-39 v heads
+        float x[8];
+        raw[i].unpack(x);
+        if (row < kNHead) {  // (both halves of the warp are on the same side of every row-kind boundary)
+            pf_norm_rope8(x, wq, cs, sn, rope, sc);
+            pf_store_half44(a.q_st + (size_t(row) * a.n_tok + t) * kHeadDim + 4 * sub, x);
+            continue;
+        }
+        const bool is_k = row < kNHead + kNHeadKv;
+        const int kvh = (row - kNHead) & (kNHeadKv - 1);
+        if (is_k) {  // two of a token's twenty row pairs: the k weights are fetched here, not held all along
+            const float4 k0 = __ldg(reinterpret_cast<const float4 *>(a.k_norm) + sub);
+            const float4 k1 = __ldg(reinterpret_cast<const float4 *>(a.k_norm) + 16 + sub);
+            const float wk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+            pf_norm_rope8(x, wk, cs, sn, rope, 1.0f);
+        }
+        if (to_cache) {
             __half *cache = is_k ? a.k_cache : a.v_cache;
-            const size_t row = a.block_table ? (page * kNHeadKv + kvh) * 64 + (pos & 63) : size_t(kvh) * a.n_slots + slot;
-            pf_store_half4(cache + row * kHeadDim + 4 * lane, y);
+            const size_t crow = a.block_table ? (page * kNHeadKv + kvh) * 64 + (pos & 63) : size_t(kvh) * a.n_slots + slot;
+            pf_store_half44(cache + crow * kHeadDim + 4 * sub, x);
         }
         if (a.k_st) {
             __half *st = is_k ? a.k_st : a.v_st;
-            pf_store_half4(st + (size_t(kvh) * (a.n_hist + a.n_tok) + a.n_hist + t) * kHeadDim + 4 * lane, y);
+            pf_store_half44(st + (size_t(kvh) * (a.n_hist + a.n_tok) + a.n_hist + t) * kHeadDim + 4 * sub, x);
         }
     }
+}
+
+// History pass (ring layers with p0 > 0): one warp per (history row, kv head) copies the up to 512 keys before p0 out
+// of the ring into the linear staging the attention kernel reads.  The history pass is its own, earlier launch: tokens
+// p0+512.. of a long prompt land in the very ring slots the history occupies (which is why the reference prefills in
+// chunks of at most 512, src/metal/flint_config.h:29-31).
+__global__ void __launch_bounds__(256) k_prefill_history(const PrologueArgs a) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * 8 + warp;
+    if (row >= (long long)a.n_hist * kNHeadKv) return;
+    const int r = int(row / kNHeadKv), kvh = int(row % kNHeadKv);
+    const int pos = a.p0 - a.n_hist + r, slot = pos & (kSwaRing - 1);
+    const size_t src = (size_t(kvh) * a.n_slots + slot) * kHeadDim + 4 * lane;
+    const size_t dst = (size_t(kvh) * (a.n_hist + a.n_tok) + r) * kHeadDim + 4 * lane;
+    *reinterpret_cast<uint2 *>(a.k_st + dst) = *reinterpret_cast<const uint2 *>(a.k_cache + src);
+    *reinterpret_cast<uint2 *>(a.v_st + dst) = *reinterpret_cast<const uint2 *>(a.v_cache + src);
+}
+
+// (one kernel per input type: the bf16 one holds half the registers in flight and fits eight CTAs on an SM)
+template <bool kBf16>
+__global__ void __launch_bounds__(128, kBf16 ? 8 : 5) k_prefill_prologue(const PrologueArgs a) {
+    // the attention kernel of this prefill may be scheduled as soon as SMs come free: it waits for this grid's
+    // completion (griddepcontrol.wait) before it reads anything written here
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    prologue_rows<kBf16>(a);
 }
 
 // ------------------------------------------------------------------------------------------------- attention
@@ -342,6 +408,10 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             tc5::prefetch_tmap(&tm_q);
             tc5::prefetch_tmap(&tm_k);
             tc5::prefetch_tmap(&tm_v);
+            // Programmatic dependent launch: this kernel may have been scheduled while the prologue still ran.  Nothing
+            // the prologue writes (staged q, K/V staging, cache rows) is read before this wait, and every other warp of
+            // the CTA only ever works on what this thread's loads bring in.
+            asm volatile("griddepcontrol.wait;\n" ::: "memory");
             int g = 0;  // tiles sent through the ring so far
             auto load_tile = [&](const CUtensorMap *map, const Unit &un, int kt) {
                 const int slot = g % kSlots, use = g / kSlots;
@@ -904,20 +974,25 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
     pa.kv_lo = p.is_swa ? 0 : p.kv_lo;
     pa.kv_hi = p.is_swa ? 0x7fffffff : p.kv_hi;
     cudaError_t e;
-    if (n_hist > 0) {
-        pa.history_pass = 1;
-        k_prefill_prologue<<<unsigned((n_hist * kNHeadKv + 7) / 8), 256, 0, stream>>>(pa);
-        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    // The prologue is launched last, directly in front of the attention kernel, so that the two are neighbours on the
+    // stream: the attention kernel is launched with programmatic stream serialisation and sets itself up (tensor
+    // memory, barriers, work list) on SMs the prologue has already left.
+    auto launch_prologue = [&]() -> cudaError_t {
+        if (n_hist > 0) {
+            k_prefill_history<<<unsigned((n_hist * kNHeadKv + 7) / 8), 256, 0, stream>>>(pa);
+            if (cudaError_t le = cudaGetLastError(); le != cudaSuccess) return le;
+            (*n_launches)++;
+        }
+        if (pa.qkv_dtype == kDtypeBf16) k_prefill_prologue<true><<<unsigned(T), 128, 0, stream>>>(pa);
+        else k_prefill_prologue<false><<<unsigned(T), 128, 0, stream>>>(pa);
+        if (cudaError_t le = cudaGetLastError(); le != cudaSuccess) return le;
         (*n_launches)++;
-    }
-    pa.history_pass = 0;
-    k_prefill_prologue<<<unsigned(((long long)T * 5 + 7) / 8), 256, 0, stream>>>(pa);
-    if ((e = cudaGetLastError()) != cudaSuccess) return e;
-    (*n_launches)++;
+        return cudaSuccess;
+    };
 
     if (cp) {  // rows whose unit has no key on this device are never written: they must read as empty parts
         if ((e = cudaMemsetAsync(p.partial_ml, 0, size_t(T) * kNHead * sizeof(float2), stream)) != cudaSuccess) return e;
-        if (n_units_q == 0) return cudaSuccess;
+        if (n_units_q == 0) return launch_prologue();
     }
     CUtensorMap tm_q, tm_k, tm_v, tm_o;
     if (n_ksplit > 1) e = make_out_map(&tm_o, part_o, n_ksplit * t_pad, kDtypeF32);  // partials: fp32, un-normalised
@@ -961,9 +1036,25 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
         a.sched = ws.sched;
         a.n_rounds = ws.sched_rounds;
     }
+    if ((e = launch_prologue()) != cudaSuccess) return e;
     if (p.ev_attn_begin && (e = cudaEventRecord(p.ev_attn_begin, stream)) != cudaSuccess) return e;
-    k_prefill_attn<<<grid, kThreadsAttn, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_o, a);
-    e = cudaGetLastError();
+    {
+        static const bool no_pdl = [] {
+            const char *v = getenv("FLINT_ATTN_NO_PDL");
+            return v && v[0] == '1';
+        }();
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreadsAttn);
+        cfg.dynamicSmemBytes = kSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = no_pdl ? 0 : 1;
+        e = cudaLaunchKernelEx(&cfg, k_prefill_attn, tm_q, tm_k, tm_v, tm_o, a);
+    }
     if (e != cudaSuccess) return e;
     (*n_launches)++;
     if (n_ksplit > 1) {

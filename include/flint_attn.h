@@ -32,7 +32,8 @@ extern "C" {
 
 typedef struct flint_attn flint_attn;
 
-/* Element types of the qkv input rows and of the attention output rows. */
+/* Element types of the qkv input rows and of the attention output rows.  Row buffers start on a 16-byte boundary
+ * (any device allocation does; so does every row of one, a row being 10240 or 20480 bytes). */
 enum { FLINT_ATTN_F32 = 0, FLINT_ATTN_BF16 = 1 };
 
 enum {
