@@ -38,15 +38,15 @@ constexpr int kBM = kQPos * kGqa;      // 128 query rows per Q tile
 constexpr int kQTiles = 2;             // Q tiles per CTA: they share every K/V tile and take turns on the tensor core
 constexpr int kCtaPos = kQPos * kQTiles;  // 32 query positions per CTA
 constexpr int kBN = 128;               // keys per tile: an MMA narrower than N = 128 runs at half rate
-constexpr int kSlots = 3;              // ring of 32 KiB tile slots, used alternately for K and V tiles
+constexpr int kSlots = 3;              // 32 KiB tile slots: slot 0 takes every K tile in turn, slots 1 and 2 the V tiles alternately
 constexpr int kHist = kNSwa - 1;       // 512 keys of history a sliding-window query can see
 // Tensor memory (all 512 columns): scores S per Q tile (read into registers, then free for the next tile's scores) and the
 // output accumulators.
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0;               // + 128 * tile
 constexpr int kColO = 256;             // + 128 * tile
-constexpr int kThreadsAttn = (kQTiles * 4 + 4) * 32;  // 8 softmax warps, 1 TMA warp, 1 MMA warp, 2 idle warps that
-                                                      // complete the third warpgroup (register reallocation is per warpgroup)
+constexpr int kThreadsAttn = (kQTiles * 4 + 4) * 32;  // 8 softmax warps, 1 TMA warp, 2 MMA warps, 1 idle warp that
+                                                      // completes the third warpgroup (register reallocation is per warpgroup)
 
 constexpr int kQBytes = kBM * kHeadDim * 2;   // 32 KiB per Q tile: two 64-dim halves of [128 rows][128 B]
 constexpr int kTileBytes = kBN * kHeadDim * 2;  // 32 KiB per K or V tile: two 64-dim halves of [128 keys][128 B]
@@ -372,6 +372,8 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
     }
     auto bar = [&](int i) { return base + kOffBar + 8u * uint32_t(i); };
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + kOffBar + 8 * kNumBars);
+    volatile int *pace = reinterpret_cast<volatile int *>(gen + kOffBar + 8 * kNumBars + 8);  // units whose first tile Q tile 0 is through
+    static_assert(8 * kNumBars + 16 <= 256, "barrier block");
 
     const int tid = threadIdx.x, warp = tid >> 5;
     int *sched_local = reinterpret_cast<int *>(gen + kOffSched);
@@ -380,9 +382,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             sched_local[i] = a.sched[size_t(i) * gridDim.x + blockIdx.x];
 
     if (tid == 0) {
+        *pace = 0;
         for (int i = 0; i < kNumBars; i++) {
             const bool many = (i >= kBarPReady && i < kBarPReady + 2) || (i >= kBarOFree && i < kBarOFree + 4);
-            tc5::mbar_init(bar(i), many ? kBM : 1);
+            const bool pair = i >= kBarSlotEmpty && i < kBarSlotEmpty + kSlots;  // one commit from each MMA issuer
+            tc5::mbar_init(bar(i), many ? kBM : pair ? kQTiles : 1);
         }
         tc5::mbar_fence_init();
     }
@@ -398,8 +402,8 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
 
     // Three warps share each SM sub-partition's 16K registers: the compiler's budget is 168 per thread.  The softmax
     // rows want ~200 (a whole 128-column score row in registers), the TMA / MMA warps few: move registers over.
-    // (each role executes its own setmaxnreg first thing; warps 10 and 11 only complete the third warpgroup)
-    if (warp >= 10) {
+    // (each role executes its own setmaxnreg first thing; warp 11 only completes the third warpgroup)
+    if (warp >= 11) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
     } else if (warp == 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
@@ -414,7 +418,12 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             asm volatile("griddepcontrol.wait;\n" ::: "memory");
             int g = 0;  // tiles sent through the ring so far
             auto load_tile = [&](const CUtensorMap *map, const Unit &un, int kt) {
-                const int slot = g % kSlots, use = g / kSlots;
+                // K of stream tile jt is done with as soon as both Q.K^T products of that tile are, early in the step;
+                // V of tile jt only after its P.V products, a whole softmax later.  One slot that turns over every
+                // step for K and two that alternate for V let K of tile jt+2 come in while V of tile jt is still
+                // waited on, which a single ring through all three slots would not.
+                const int jt = g >> 1;
+                const int slot = (g & 1) ? 1 + (jt & 1) : 0, use = (g & 1) ? jt >> 1 : jt;
                 g++;
                 if (use >= 1 && !wait_bar(bar(kBarSlotEmpty + slot), (use - 1) & 1)) return false;
                 const uint32_t dst = base + kOffKV + slot * kTileBytes, full = bar(kBarSlotFull + slot);
@@ -458,19 +467,25 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             }
             if (!ok) atomicExch(a.error_flag, 1);
         }
-    } else if (warp == 9) {
+    } else if (warp == 9 || warp == 10) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 88;\n");
-        // =========================================================== MMA issuer (warp-uniform code, one lane issues)
+        // =========================================================== MMA issuers (warp-uniform code, one lane issues)
+        // One issuer per Q tile: warp 9 for tile 0, warp 10 for tile 1.  Each walks the same stream of key tiles and
+        // waits only on its own tile's softmax, so a tile whose softmax runs behind the other's never holds up the
+        // other's products: the two tiles drift half a step apart, and one tile's exponentials (the special-function
+        // unit) run under the other's loads, maxima and waits instead of at the same time.
+        const int w = warp - 9;
         const uint32_t leader = (tid & 31) == 0;
         constexpr uint32_t kDescHi = tc5::desc_hi_sw128(1024);
-        constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);  // A = P (tensor memory), B = V (MN-major)
-        const uint32_t q_lo = tc5::desc_lo(base + kOffQ, 16);
-        const uint32_t p_lo = tc5::desc_lo(base + kOffStage, 16);            // P tile: K-major, two 64-key halves
+        constexpr uint32_t kIdescPV = tc5::idesc_f16(kBM, kHeadDim, 0, 1);  // A = P (shared memory), B = V (MN-major)
+        const uint32_t q_lo = tc5::desc_lo(base + kOffQ, 16) + w * (kQBytes >> 4);
+        const uint32_t p_lo = tc5::desc_lo(base + kOffStage, 16) + w * (kPBytes >> 4);  // P tile: K-major, two 64-key halves
         const uint32_t k_lo = tc5::desc_lo(base + kOffKV, 16);               // K tile: K-major, two 64-dim halves
         const uint32_t v_lo = tc5::desc_lo(base + kOffKV, kTileBytes / 2);   // V tile: MN-major, LBO = the other 64 dims
-        // The key tiles of all units of this CTA form one stream; tile j of the stream has its K in ring use 2j and
-        // its V in ring use 2j + 1.  For each tile and Q tile w: P.V, then Q.K^T of the NEXT tile of the stream (S of w
-        // is free again: its P is consumed by the product just issued, in order), possibly of the next unit.
+        // The key tiles of all units of this CTA form one stream; tile j of the stream has its K in slot 0 (use j) and
+        // its V in slot 1 + j % 2 (use j / 2).  For each tile: Q.K^T of the NEXT tile of the stream (S is free again as
+        // soon as the softmax has read the current scores into registers), possibly of the next unit, then P.V of the
+        // current one when its P has been written.
         struct Cursor {
             int i, kt, j;  // index of the unit in this CTA's list, tile in the unit, tile in the stream
             Unit un;
@@ -490,59 +505,54 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             c.j++;
             return true;
         };
-        auto issue_qk = [&](int w, const Cursor &c) {
-            const int g = 2 * c.j, slot = g % kSlots;
+        auto issue_qk = [&](const Cursor &c) {
+            const int slot = 0;
             if (c.j >= 1 && !wait_bar(bar(kBarSFree + w), (c.j - 1) & 1)) return false;  // the previous scores are read out
             if (c.kt == 0 && !wait_bar(bar(kBarQFull + w), c.i & 1)) return false;
-            if (w == 0 && !wait_bar(bar(kBarSlotFull + slot), (g / kSlots) & 1)) return false;
+            if (!wait_bar(bar(kBarSlotFull + slot), c.j & 1)) return false;
             tc5::fence_after_sync();
             const uint32_t kst = k_lo + uint32_t(slot) * (kTileBytes >> 4);
             const uint32_t idesc = tc5::idesc_f16(kBM, tile_n(c), 0, 0);  // A = Q (K-major), B = K (K-major)
 #pragma unroll
             for (int ks = 0; ks < kHeadDim / 16; ks++) {
                 const uint32_t off = (ks >> 2) * ((kTileBytes / 2) >> 4) + (ks & 3) * 2;  // Q and K halves are both 16 KiB
-                tc5::mma_f16_ss_lohi_w(tmem + kColS + w * kBN, q_lo + w * (kQBytes >> 4) + off, kst + off, kDescHi, idesc,
-                                       ks > 0, leader);
+                tc5::mma_f16_ss_lohi_w(tmem + kColS + w * kBN, q_lo + off, kst + off, kDescHi, idesc, ks > 0, leader);
             }
             tc5::mma_commit_w(bar(kBarSReady + w), leader);
             if (c.kt == c.un.n_tiles - 1) tc5::mma_commit_w(bar(kBarQEmpty + w), leader);  // last use of this Q tile
-            if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);     // both Q tiles read this K
+            tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);  // (the slot is free when both issuers have said so)
             return true;
         };
-        auto issue_pv = [&](int w, const Cursor &c) {
-            const int g = 2 * c.j + 1, slot = g % kSlots;
+        auto issue_pv = [&](const Cursor &c) {
+            const int slot = 1 + (c.j & 1);
             if (!wait_bar(bar(kBarPReady + w), c.j & 1)) return false;
             if (c.kt == 0 && c.i >= 1 && !wait_bar(bar(kBarOFree + w), (c.i - 1) & 1)) return false;
-            if (w == 0 && !wait_bar(bar(kBarSlotFull + slot), (g / kSlots) & 1)) return false;
+            if (!wait_bar(bar(kBarSlotFull + slot), (c.j >> 1) & 1)) return false;
             tc5::fence_after_sync();
             const uint32_t vst = v_lo + uint32_t(slot) * (kTileBytes >> 4);
             const int n_steps = tile_n(c) / 16;
 #pragma unroll
             for (int ks = 0; ks < kBN / 16; ks++)
                 if (ks < n_steps)
-                    tc5::mma_f16_ss_lohi_w(tmem + kColO + w * kHeadDim,
-                                           p_lo + w * (kPBytes >> 4) + (ks >> 2) * ((kPBytes / 2) >> 4) + (ks & 3) * 2,
+                    tc5::mma_f16_ss_lohi_w(tmem + kColO + w * kHeadDim, p_lo + (ks >> 2) * ((kPBytes / 2) >> 4) + (ks & 3) * 2,
                                            vst + ks * (2048 >> 4), kDescHi, kIdescPV, (c.kt > 0 || ks > 0), leader);
             tc5::mma_commit_w(bar(kBarPvDone + w), leader);
-            if (w == kQTiles - 1) tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);
+            tc5::mma_commit_w(bar(kBarSlotEmpty + slot), leader);
             return true;
         };
         if (unit_at(a, sched_local, 0) >= 0) {
             Cursor cur{0, 0, 0, unit_geom(a, unit_at(a, sched_local, 0))};
-            ok = issue_qk(0, cur) && issue_qk(1, cur);
+            ok = issue_qk(cur);
             while (ok) {
                 Cursor nxt = cur;
                 const bool more = advance(nxt);
                 // The next scores are issued as soon as the current ones have been read into registers, so they are
-                // computed while the softmax of the current tile runs; P.V follows when P has been written.
-#pragma unroll
-                for (int w = 0; w < kQTiles; w++) {
-                    if (more) ok = ok && issue_qk(w, nxt);
-                }
-#pragma unroll
-                for (int w = 0; w < kQTiles; w++) {
-                    ok = ok && issue_pv(w, cur);
-                }
+                // computed while the softmax of the current tile runs; P.V follows when P has been written.  Across a
+                // unit boundary the order turns round: the next unit's Q tile is still on its way, and the last P.V is
+                // what the softmax warps wait for before they can write the unit out.
+                if (more && nxt.kt != 0) ok = issue_qk(nxt);
+                ok = ok && issue_pv(cur);
+                if (more && nxt.kt == 0) ok = ok && issue_qk(nxt);
                 if (!more) break;
                 cur = nxt;
             }
@@ -664,6 +674,17 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
                 tc5::tmem_wait_st();
                 tc5::fence_before_sync();
             }
+            // The two Q tiles work half a step apart.  A tile's exponentials alone keep the special-function unit
+            // busy; when both tiles run them at once each takes twice as long, and the unit then idles through both
+            // tiles' loads, maxima and waits.  With its own MMA issuer a tile that runs behind stays behind, so it is
+            // enough to hold tile 1 back once per unit: it starts its first exponentials of the unit when tile 0 has
+            // finished its own.  This is pacing only: the wait gives up after a few microseconds and nothing depends
+            // on it.
+            if (w == 1 && kt == 0) {
+                const long long t_pace = clock64();
+                while (*pace < i + 1 && clock64() - t_pace < 16384) {
+                }
+            }
             // probabilities: P (half) goes to this Q tile's shared-memory block in the K-major 128-byte-swizzled layout
             // of an MMA A operand: two 64-key halves of [128 rows][128 B]
             // A row that has not seen a visible key yet (a key-range shard that starts after its position) still has
@@ -694,6 +715,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             tc5::fence_proxy_async();
             tc5::mbar_arrive(bar(kBarPReady + w));
+            if (w == 0 && kt == 0 && r == 0) *pace = i + 1;
             j++;
         }
         // ---- drain of the unit.  The scores of the last tile proved P.V of the tile before it done, so a parity wait
