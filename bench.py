@@ -35,8 +35,8 @@ L2_BYTES = 126 << 20
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from an ncu capture of one launch of the
 # workload on this part: the decode kernel on 64 sequences x 8192 cached tokens, and the prefill attention kernel on
 # the 4000-token sliding-window prompt.  --traffic-from replaces the decode figure with one read from an ncu CSV.
-DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1074846000 + 5344512
-PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41032192 + 1581056
+DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1082838000 + 4117760
+PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41043712 + 1458176
 DECODE_WORKLOAD = ("decode: 64 seqs x 8192 cached tokens, 1 full layer, 32q/4kv heads x 128, bf16 qkv rows, "
                    "fp16 KV cache, norm+RoPE+KV write fused")
 

@@ -80,8 +80,11 @@ struct PlanCache {
     std::vector<DecItem> items;
 };
 
-void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi, int target_items,
-                 std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs, PlanScratch &ps) {
+// One planning pass for a given number of CTA slots.  Returns the longest item's keys; `total_rows` gets the cached
+// rows summed over all (sequence, KV head) groups.
+static int plan_decode_for(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi,
+                           int target_items, std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs,
+                           PlanScratch &ps, long long &total_rows) {
     long long total = 0;
     ps.lo.resize(n);
     ps.hi.resize(n);
@@ -93,6 +96,7 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
         total += hi[i] - lo[i];
     }
     total *= kNHeadKv;
+    total_rows = total;
     if (target_items < 1) target_items = 1;
     // A window of at most 512 cached keys is never split: two 256-key items plus their merge take longer than one
     // 512-key item (12.4 vs 10.3 us per launch for 32 sequences).  Full layers split down to 256 keys: there a lone
@@ -119,7 +123,7 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
     std::vector<DecItem> &gen = items;  // generated in place; reordered below only when needed
     gen.clear();
     bool sorted = true;  // already longest first?
-    int prev_len = INT32_MAX;
+    int prev_len = INT32_MAX, max_len = 0;
     for (int i = 0; i < n; i++) {
         const int nk = hi[i] - lo[i];
         const bool own_new = kv_lo <= pos[i] && pos[i] < kv_hi;
@@ -149,12 +153,13 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
                 const int len = it.j1 - it.j0;
                 sorted = sorted && len <= prev_len;
                 prev_len = len;
+                max_len = std::max(max_len, len);
                 gen.push_back(it);
             }
         }
     }
     // longest first: the block scheduler hands CTAs out in order, which makes this a greedy LPT schedule
-    if (sorted) return;
+    if (sorted) return max_len;
     const size_t m = items.size();
     ps.keys.resize(m);
     for (size_t i = 0; i < m; i++)  // ascending key = descending length, ties in generation order
@@ -162,6 +167,24 @@ void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, in
     std::sort(ps.keys.begin(), ps.keys.end());
     ps.gen.assign(items.begin(), items.end());
     for (size_t i = 0; i < m; i++) items[i] = ps.gen[uint32_t(ps.keys[i])];
+    return max_len;
+}
+
+// The work list of one decode launch.  A batch of equal sequences is cut into one wave of items (every item pays a
+// few microseconds of start-up and merge: 8 x 8192 keys take 33 us as 128-288 items, 38-40 us as 384-592).  A ragged
+// batch cut that way leaves one item per slot with lengths up to 1.5x the mean, and the launch lasts as long as its
+// longest item; when the longest item of the one-wave list exceeds the mean slot load by more than a fifth the list
+// is planned again for two waves of shorter items, which the longest-first order packs well (32 sequences of 1..32768
+// keys: 190 -> 166 us; 64 such sequences: 405 -> 319 us; three or more waves are slower again).
+void plan_decode(int n, const int32_t *seqs, const int32_t *pos, bool is_swa, int kv_lo, int kv_hi, int target_items,
+                 std::vector<DecItem> &items, int &n_groups, int &n_records, int &n_subs, PlanScratch &ps) {
+    long long total = 0;
+    if (target_items < 1) target_items = 1;
+    const int max_len = plan_decode_for(n, seqs, pos, is_swa, kv_lo, kv_hi, target_items, items, n_groups, n_records,
+                                        n_subs, ps, total);
+    if (!is_swa && n * kNHeadKv <= target_items && (long long)max_len * target_items * 5 > total * 6)
+        plan_decode_for(n, seqs, pos, is_swa, kv_lo, kv_hi, 2 * target_items, items, n_groups, n_records, n_subs, ps,
+                        total);
 }
 
 // Brings a cached work list to the positions `pos` when they equal the cached ones or are all one ahead, and nothing
