@@ -69,6 +69,24 @@ def test_plan_covers_every_key_exactly_once(fa, fo, is_swa, target):
         recs.add(r)
 
 
+def test_plan_waves(fa):
+    """Equal sequences are cut into one wave of work items; a ragged batch whose one-wave list would leave its longest
+    item well above the mean slot load gets two waves of shorter items (and never more)."""
+    slots = 296
+    for n, ctx in ((8, 8192), (16, 8192), (32, 8192), (64, 8192), (4, 8192), (1, 131072)):
+        items = fa.plan_decode([ctx] * n, False, target_items=slots)
+        assert len(items) <= slots, (n, ctx, len(items))
+    rng = np.random.default_rng(7)
+    ragged = [int(x) for x in rng.integers(1, 32769, 32)]
+    items = fa.plan_decode(ragged, False, target_items=slots)
+    lengths = items[:, 3] - items[:, 2]
+    assert slots < len(items) <= 2 * slots
+    mean_slot = 4 * sum(ragged) / slots
+    assert lengths.max() <= mean_slot            # no item longer than a slot's share of one wave
+    # sliding-window layers are never re-planned: one item per (sequence, KV head)
+    assert len(fa.plan_decode(ragged, True, target_items=slots)) == 4 * len(ragged)
+
+
 def test_plan_with_kv_range_sharding(fa, fo):
     pos = [0, 100, 4999, 5000, 5001, 9999]
     shards = [(0, 5000), (5000, 10000)]
