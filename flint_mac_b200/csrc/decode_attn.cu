@@ -197,6 +197,13 @@ __device__ __forceinline__ void publish_group(const DecParams &p, int tid) {
     }
 }
 
+// Takes a ticket: returns the old count.  Acquire-release at device scope (see the split-K merge).
+__device__ __forceinline__ int ticket_acq_rel(int *counter) {
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;\n" : "=r"(old) : "l"(counter) : "memory");
+    return old;
+}
+
 // Fold n partial records of one head (fused.metal:332-350) into the running state (M, L, a): M = max m_s,
 // L = sum l_s e^(m_s - M), a = sum acc_s e^(m_s - M); the sink enters as a record with m = sink, l = 1, acc = 0.
 // `rec` points at record 0 of this thread's head; consecutive records of the same head are kGqa * kRecStride floats
@@ -325,6 +332,10 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     // parameters and the layer's constant tables; nothing produced by an earlier kernel (the q/k/v rows, cache
     // contents, split-K scratch and counters) is read or written before this wait, which returns once every
     // earlier kernel of the stream has completed and its writes are visible.
+    if (kTma && tid == 0) {  // the maps are written once, when the handle is opened: fetching them early is safe
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(p.k_map)) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(p.v_map)) : "memory");
+    }
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     if (kTma && tid == 0) {
 #pragma unroll
@@ -553,17 +564,15 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
     // each run of 16 splits folds those records into one; the last of those to finish folds the runs and the sink.
     const int sub = it.split / kMergeFan, n_sub = (it.n_split + kMergeFan - 1) / kMergeFan;
     const int sub_size = min(kMergeFan, it.n_split - sub * kMergeFan);
-    // The CTA's record stores are ordered before thread 0's fence by the barrier, and the fence is cumulative, so
-    // one thread publishes for all; on the reading side its second fence plus the barrier cover the other threads,
-    // which read the records past L1 (ld.cg).
+    // The CTA's record stores are ordered before thread 0's ticket by the barrier, and the ticket is an acquire-release
+    // atomic at device scope: its release side is cumulative, so one thread publishes for all; its acquire side plus
+    // the second barrier cover the other threads, which read the records past L1 (ld.cg).  (A fence either side of a
+    // relaxed atomic does the same but makes the last arriver wait twice more for a round trip to L2, the second time
+    // for its own reset of the ticket.)
     __syncthreads();
     if (tid == 0) {
-        __threadfence();
-        const bool last = atomicAdd(&p.tickets[it.sub0 + sub], 1) == sub_size - 1;
-        if (last) {
-            p.tickets[it.sub0 + sub] = 0;  // ready for the next launch
-            __threadfence();
-        }
+        const bool last = ticket_acq_rel(&p.tickets[it.sub0 + sub]) == sub_size - 1;
+        if (last) p.tickets[it.sub0 + sub] = 0;  // ready for the next launch; nothing in this one waits for it
         sm.is_last = last;
     }
     __syncthreads();
@@ -583,12 +592,8 @@ __device__ __forceinline__ void decode_item(const DecParams &p, const DecItem &i
         if (md == 0) { rec2[kHeadDim] = r.M; rec2[kHeadDim + 1] = r.L; }
         __syncthreads();
         if (tid == 0) {
-            __threadfence();
-            const bool last = atomicAdd(&p.tickets2[it.group], 1) == n_sub - 1;
-            if (last) {
-                p.tickets2[it.group] = 0;
-                __threadfence();
-            }
+            const bool last = ticket_acq_rel(&p.tickets2[it.group]) == n_sub - 1;
+            if (last) p.tickets2[it.group] = 0;
             sm.is_last = last;
         }
         __syncthreads();

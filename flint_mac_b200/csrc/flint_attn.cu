@@ -105,11 +105,12 @@ static int plan_decode_for(int n, const int32_t *seqs, const int32_t *pos, bool 
     int chunk = round_up(int(std::max<long long>(min_chunk, (total + target_items - 1) / target_items)), 64);
     // Rounding every group to its nearest number of splits can overshoot the target (64 groups x 5 splits = 320 items
     // for 296 slots: a second wave that nearly doubles the launch).  If it does, the chunk grows until the list fits.
+    auto splits_of = [](int nk, int c) { return std::max(1, (nk + c / 2) / c); };  // the nearest count
     auto count_items = [&](int c) {
         long long items = 0;
         for (int i = 0; i < n; i++) {
             const int nk = hi[i] - lo[i];
-            int n_split = std::max(1, (nk + c / 2) / c);
+            int n_split = splits_of(nk, c);
             const int per = std::max(64, round_up((nk + n_split - 1) / n_split, 64));
             items += std::max(1, (nk + per - 1) / per);
         }
@@ -127,7 +128,7 @@ static int plan_decode_for(int n, const int32_t *seqs, const int32_t *pos, bool 
     for (int i = 0; i < n; i++) {
         const int nk = hi[i] - lo[i];
         const bool own_new = kv_lo <= pos[i] && pos[i] < kv_hi;
-        int n_split = std::max(1, (nk + chunk / 2) / chunk);
+        int n_split = splits_of(nk, chunk);
         const int per = std::max(64, round_up((nk + n_split - 1) / n_split, 64));
         n_split = std::max(1, (nk + per - 1) / per);
         for (int kvh = 0; kvh < kNHeadKv; kvh++) {
