@@ -267,16 +267,15 @@ __global__ void __launch_bounds__(128, kBf16 ? 8 : 5) k_prefill_prologue(const P
 
 // ------------------------------------------------------------------------------------------------- attention
 __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
-    // Bounded: gives up after ~2^29 SM cycles (a quarter of a second), far beyond anything a healthy launch needs.
-    // The cycle counter is SM-local and cheap to read, and it is only looked at every 64 polls.
-    if (tc5::mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
+    // Bounded by a count of polls, not by the clock: 2^24 polls are a quarter of a second when every poll returns at
+    // once and longer when the hardware suspends the thread inside a poll, far beyond anything a healthy launch needs
+    // (a launch may sit behind its predecessor on the stream for a while).  The loop is four instructions; with a
+    // clock read and a second loop around it, inlined at some twenty waits, the kernel ran 3-4 % slower: its softmax
+    // warps are short of instruction-cache, not of issue slots.
 #pragma unroll 1
-        for (int i = 0; i < 64; i++)
-            if (tc5::mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > (1ll << 29)) return false;
-    }
+    for (uint32_t n = 0; n < (1u << 24); n++)
+        if (tc5::mbar_try_wait(bar, parity)) return true;
+    return false;
 }
 
 // Packed two-float arithmetic (sm_100): a 64-bit register holds two floats.
