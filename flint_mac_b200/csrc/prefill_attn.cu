@@ -87,6 +87,36 @@ struct PfArgs {
 };
 
 // ------------------------------------------------------------------------------------------------- prologue
+// Packed two-float arithmetic (sm_100): a 64-bit register holds two floats.
+__device__ __forceinline__ unsigned long long pack_f32x2(float a, float b) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float &a, float &b) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
+}
+// (a, b) - m2, the operands given as float bit patterns
+__device__ __forceinline__ void sub_f32x2(uint32_t a, uint32_t b, unsigned long long m2, float &o0, float &o1) {
+    asm("{\n.reg .b64 x, z;\nmov.b64 x, {%2, %3};\nsub.rn.f32x2 z, x, %4;\nmov.b64 {%0, %1}, z;\n}\n"
+        : "=f"(o0), "=f"(o1)
+        : "r"(a), "r"(b), "l"(m2));
+}
+__device__ __forceinline__ void add_f32x2(unsigned long long &acc, float a, float b) {
+    asm("{\n.reg .b64 x;\nmov.b64 x, {%1, %2};\nadd.rn.f32x2 %0, %0, x;\n}\n" : "+l"(acc) : "f"(a), "f"(b));
+}
+
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 struct PrologueArgs {
     const void *qkv;
     const float *q_norm, *k_norm, *inv_freq;
@@ -139,27 +169,39 @@ __device__ __forceinline__ void pf_store_half44(__half *dst, const float (&v)[8]
     *reinterpret_cast<uint2 *>(dst + kHeadDim / 2) = make_uint2(pack_half2(v[4], v[5]), pack_half2(v[6], v[7]));
 }
 
-// RMSNorm with weight, then NEOX RoPE with this token's (cos, sin) per owned pair of dims (same arithmetic as
-// src/ref/ref_model.cpp:45-61; `extra` is 1 for keys).  A row of 128 lives in 16 lanes; the two halves of a warp hold
-// two different rows.  x[j] and x[j + 4] are dims d and d + 64.
-__device__ __forceinline__ void pf_norm_rope8(float (&x)[8], const float (&w)[8], const float (&cs)[4],
-                                              const float (&sn)[4], bool rope, float extra) {
-    float ss = 0.f;
+// RMSNorm with weight, then NEOX RoPE with this token's (cos, sin) per owned pair of dims (the arithmetic of
+// src/ref/ref_model.cpp:45-61; `extra` is 1 for keys), in packed two-float instructions: the kernel is bound by
+// instruction issue.  A row of 128 lives in 16 lanes; the two halves of a warp hold two different rows.  x[j] and
+// x[j + 4] are dims d and d + 64; cs2 / sn2 / nsn2 hold (cos, cos'), (sin, sin') and (-sin, -sin') of dims (d, d + 1)
+// and (d + 2, d + 3); w2 the norm weights of dims (d, d+1), (d+2, d+3), (d+64, d+65), (d+66, d+67).
+__device__ __forceinline__ void pf_norm_rope8(float (&x)[8], const unsigned long long (&w2)[4],
+                                              const unsigned long long (&cs2)[2], const unsigned long long (&sn2)[2],
+                                              const unsigned long long (&nsn2)[2], bool rope, float extra) {
+    unsigned long long v[4];
 #pragma unroll
-    for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+    for (int i = 0; i < 4; i++) v[i] = pack_f32x2(x[2 * i], x[2 * i + 1]);
+    unsigned long long acc = mul_f32x2(v[0], v[0]);
+#pragma unroll
+    for (int i = 1; i < 4; i++) acc = fma_f32x2(v[i], v[i], acc);
+    float s0, s1;
+    unpack_f32x2(acc, s0, s1);
+    float ss = s0 + s1;
 #pragma unroll
     for (int off = 1; off < 16; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
     const float scale = 1.0f / sqrtf(ss / kHeadDim + kRmsEps) * extra;
+    const unsigned long long scale2 = pack_f32x2(scale, scale);
 #pragma unroll
-    for (int j = 0; j < 8; j++) x[j] = x[j] * scale * w[j];
+    for (int i = 0; i < 4; i++) v[i] = mul_f32x2(mul_f32x2(v[i], scale2), w2[i]);
     if (rope) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float lo = x[j], hi = x[j + 4];
-            x[j] = lo * cs[j] - hi * sn[j];
-            x[j + 4] = lo * sn[j] + hi * cs[j];
+        for (int i = 0; i < 2; i++) {  // lo' = lo cos - hi sin, hi' = lo sin + hi cos
+            const unsigned long long lo = v[i], hi = v[i + 2];
+            v[i] = fma_f32x2(hi, nsn2[i], mul_f32x2(lo, cs2[i]));
+            v[i + 2] = fma_f32x2(lo, sn2[i], mul_f32x2(hi, cs2[i]));
         }
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++) unpack_f32x2(v[i], x[2 * i], x[2 * i + 1]);
 }
 
 constexpr int kProRows = 10;  // input rows (heads) per warp: a token's 40 rows (32 q, 4 k, 4 v) take the four warps of a CTA
@@ -186,11 +228,12 @@ __device__ __forceinline__ void prologue_rows(const PrologueArgs &a) {
         sincosf(float(pos) * fr.y, &s1, &c1);
         *reinterpret_cast<float4 *>(&s_cs[2 * lane]) = make_float4(c0, s0, c1, s1);
     }
-    float wq[8];
+    unsigned long long wq[4];
     {
         const float4 q0 = __ldg(reinterpret_cast<const float4 *>(a.q_norm) + sub);
         const float4 q1 = __ldg(reinterpret_cast<const float4 *>(a.q_norm) + 16 + sub);
-        wq[0] = q0.x; wq[1] = q0.y; wq[2] = q0.z; wq[3] = q0.w; wq[4] = q1.x; wq[5] = q1.y; wq[6] = q1.z; wq[7] = q1.w;
+        wq[0] = pack_f32x2(q0.x, q0.y); wq[1] = pack_f32x2(q0.z, q0.w);
+        wq[2] = pack_f32x2(q1.x, q1.y); wq[3] = pack_f32x2(q1.z, q1.w);
     }
     const float sc = rsqrtf(float(kHeadDim)) * kLog2e;
     const int slot = a.is_swa ? (pos & (kSwaRing - 1)) : pos - a.kv_lo;  // prefill.metal:106
@@ -201,12 +244,16 @@ __device__ __forceinline__ void prologue_rows(const PrologueArgs &a) {
     // paged layer: [page][kv head][64 slots][128] instead of [kv head][slot][128]
     const size_t page = a.block_table ? size_t(a.block_table[pos >> 6]) : 0;
     __syncthreads();
-    float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    unsigned long long cs[2], sn[2], nsn[2];
+    cs[0] = cs[1] = pack_f32x2(1.f, 1.f);
+    sn[0] = sn[1] = nsn[0] = nsn[1] = pack_f32x2(0.f, 0.f);
     if (rope) {
 #pragma unroll
-        for (int j = 0; j < 4; j += 2) {
-            const float4 v = *reinterpret_cast<const float4 *>(&s_cs[4 * sub + j]);
-            cs[j] = v.x; sn[j] = v.y; cs[j + 1] = v.z; sn[j + 1] = v.w;
+        for (int j = 0; j < 2; j++) {
+            const float4 v = *reinterpret_cast<const float4 *>(&s_cs[4 * sub + 2 * j]);  // (cos, sin) of two dims
+            cs[j] = pack_f32x2(v.x, v.z);
+            sn[j] = pack_f32x2(v.y, v.w);
+            nsn[j] = pack_f32x2(-v.y, -v.w);
         }
     }
 
@@ -216,7 +263,7 @@ __device__ __forceinline__ void prologue_rows(const PrologueArgs &a) {
         float x[8];
         raw[i].unpack(x);
         if (row < kNHead) {  // (both halves of the warp are on the same side of every row-kind boundary)
-            pf_norm_rope8(x, wq, cs, sn, rope, sc);
+            pf_norm_rope8(x, wq, cs, sn, nsn, rope, sc);
             pf_store_half44(a.q_st + (size_t(row) * a.n_tok + t) * kHeadDim + 4 * sub, x);
             continue;
         }
@@ -225,8 +272,9 @@ __device__ __forceinline__ void prologue_rows(const PrologueArgs &a) {
         if (is_k) {  // two of a token's twenty row pairs: the k weights are fetched here, not held all along
             const float4 k0 = __ldg(reinterpret_cast<const float4 *>(a.k_norm) + sub);
             const float4 k1 = __ldg(reinterpret_cast<const float4 *>(a.k_norm) + 16 + sub);
-            const float wk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-            pf_norm_rope8(x, wk, cs, sn, rope, 1.0f);
+            const unsigned long long wk[4] = {pack_f32x2(k0.x, k0.y), pack_f32x2(k0.z, k0.w), pack_f32x2(k1.x, k1.y),
+                                              pack_f32x2(k1.z, k1.w)};
+            pf_norm_rope8(x, wk, cs, sn, nsn, rope, 1.0f);
         }
         if (to_cache) {
             __half *cache = is_k ? a.k_cache : a.v_cache;
@@ -276,25 +324,6 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
     for (uint32_t n = 0; n < (1u << 24); n++)
         if (tc5::mbar_try_wait(bar, parity)) return true;
     return false;
-}
-
-// Packed two-float arithmetic (sm_100): a 64-bit register holds two floats.
-__device__ __forceinline__ unsigned long long pack_f32x2(float a, float b) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
-    return r;
-}
-__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float &a, float &b) {
-    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
-}
-// (a, b) - m2, the operands given as float bit patterns
-__device__ __forceinline__ void sub_f32x2(uint32_t a, uint32_t b, unsigned long long m2, float &o0, float &o1) {
-    asm("{\n.reg .b64 x, z;\nmov.b64 x, {%2, %3};\nsub.rn.f32x2 z, x, %4;\nmov.b64 {%0, %1}, z;\n}\n"
-        : "=f"(o0), "=f"(o1)
-        : "r"(a), "r"(b), "l"(m2));
-}
-__device__ __forceinline__ void add_f32x2(unsigned long long &acc, float a, float b) {
-    asm("{\n.reg .b64 x;\nmov.b64 x, {%1, %2};\nadd.rn.f32x2 %0, %0, x;\n}\n" : "+l"(acc) : "f"(a), "f"(b));
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
