@@ -207,6 +207,34 @@ def test_short_chunks_on_a_long_full_layer_history_split_their_key_range(fa, fo)
         assert np.abs(got16 - out[hist:hist + chunks[0]]).max() <= np.abs(out).max() * 2 ** -8
 
 
+def test_short_chunks_on_a_sliding_window_history(fa, fo):
+    """The reference's call pattern (chunks of at most 512 tokens) on a sliding-window layer: a 512-token chunk behind
+    a cached prefix (64 work units whose 544-key bands start in the ring's history), then a 300-token and a 37-token
+    chunk.  Rows of every chunk against the oracle, and the ring afterwards bit for bit through V."""
+    seed, hist = 9, 1500
+    chunks = [512, 300, 37]
+    T = hist + sum(chunks)
+    w = fo.layer_weights(seed, 0)
+    qkv, bits = bf16_round_rows(fo.raw_qkv(seed, 0, 0, T))
+    with _open(fa, "swa_rope", T + 8) as h:
+        h.set_layer(0, *w)
+        out = np.zeros((T, 4096), np.float32)
+        h.prefill(0, 0, hist, bits[:hist], fa.BF16, out[:hist], fa.F32)
+        assert h.advance([0], hist) == 0
+        p = hist
+        for n in chunks:
+            h.prefill(0, 0, n, np.ascontiguousarray(bits[p:p + n]), fa.BF16, out[p:p + n], fa.F32)
+            assert h.advance([0], n) == 0
+            p += n
+        assert np.isfinite(out).all()
+        some = list(range(hist, hist + 40)) + list(range(hist + 490, hist + 530)) + list(range(T - 60, T))
+        want, _, vc = oracle_at_positions(qkv, w, True, True, some)
+        assert_close(out[some], want, "sliding-window chunks vs oracle")
+        k_dev, v_dev = h.read_kv(0, 0, 0, 1024)
+        for pos in (T - 1, T - 513, T - 1000):
+            assert np.array_equal(v_dev[:, pos % 1024].reshape(-1), fo.to_f16_bits(vc[pos])), pos
+
+
 @pytest.mark.parametrize("kind", ["swa_rope", "full_rope"])
 def test_prefill_then_decode_equals_decode_only(fa, fo, kind):
     """The reference's check-prefill idea (src/main.mm:317-346) at the kernel level: prefill the first part, decode the
