@@ -198,22 +198,37 @@ def as_tensor(torch, ptr, numel, dtype):
 
 
 # ----------------------------------------------------------------------------------------------- CPU arm
-def cpu_decode_sample(seed: int, n_sample: int, n_cached: int, n_threads: int, reps: int = 1):
-    """The oracle (src/ref arithmetic) on n_sample sequences of the decode workload; returns seconds per sequence-token."""
-    from oracle import oracle as fo
+class CpuDecodeSample:
+    """n_sample sequences of the decode workload for the oracle (src/ref arithmetic): the fp16 K/V caches are drawn once
+    (drawing 4 M normals per sequence costs ten times the attention itself); every step decodes a fresh q/k/v row on
+    each of them.  step() returns seconds per sequence-token."""
 
-    w = fo.layer_weights(seed, 0)
-    rng = np.random.default_rng(seed)
-    times = []
-    for s in range(n_sample):
-        k16 = fo.to_f16_bits(rng.standard_normal((4, n_cached + 1, 128), dtype=np.float32))
-        v16 = fo.to_f16_bits(rng.standard_normal((4, n_cached + 1, 128), dtype=np.float32))
-        row = fo.round_bf16(rng.standard_normal(QKV_DIM, dtype=np.float32))
-        for _ in range(reps):
-            t0 = time.perf_counter()
-            fo.decode_token_f16cache(row, n_cached, *w, False, True, k16, v16, n_threads=n_threads)
-            times.append(time.perf_counter() - t0)
-    return float(np.mean(times))
+    def __init__(self, seed: int, n_sample: int, n_cached: int, n_threads: int):
+        from oracle import oracle as fo
+
+        self.fo, self.n_cached, self.n_threads = fo, n_cached, n_threads
+        self.w = fo.layer_weights(seed, 0)
+        self.rng = np.random.default_rng(seed)
+        self.kv = []
+        for _ in range(n_sample):
+            k16 = fo.to_f16_bits(self.rng.standard_normal((4, n_cached + 1, 128), dtype=np.float32))
+            v16 = fo.to_f16_bits(self.rng.standard_normal((4, n_cached + 1, 128), dtype=np.float32))
+            self.kv.append((k16, v16))
+
+    def step(self, reps: int = 1) -> float:
+        fo, times = self.fo, []
+        for k16, v16 in self.kv:
+            row = fo.round_bf16(self.rng.standard_normal(QKV_DIM, dtype=np.float32))
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                fo.decode_token_f16cache(row, self.n_cached, *self.w, False, True, k16, v16, n_threads=self.n_threads)
+                times.append(time.perf_counter() - t0)
+        return float(np.mean(times))
+
+
+def cpu_decode_sample(seed: int, n_sample: int, n_cached: int, n_threads: int, reps: int = 1):
+    """One step of a fresh CpuDecodeSample; returns seconds per sequence-token."""
+    return CpuDecodeSample(seed, n_sample, n_cached, n_threads).step(reps)
 
 
 def run_reference(args):
@@ -224,12 +239,13 @@ def run_reference(args):
         return
     cores = os.cpu_count() or 1
     n_sample = 4
+    sample = CpuDecodeSample(1, n_sample, CTX, cores)
     for _ in range(args.warmup):
-        cpu_decode_sample(0, 1, CTX, cores)
+        sample.step()
     t0 = time.perf_counter()
     per_seq = []
     for k in range(args.steps):
-        per_seq.append(cpu_decode_sample(k + 1, n_sample, CTX, cores))
+        per_seq.append(sample.step())
     wall = time.perf_counter() - t0
     sec_per_seq = float(np.mean(per_seq))
     gbs = decode_bytes(1, CTX) / sec_per_seq / 1e9
