@@ -405,6 +405,9 @@ __device__ __forceinline__ int unit_at(const PfArgs &a, const int *local, int i)
 // (Q load, first scores) and the drain of the previous one (O / l, TMA store) overlap.  P goes through shared memory
 // (so the next scores can be computed while the softmax runs); every product is 128 wide (N = 128; narrower MMAs
 // run at half rate).
+// (compiled per layer kind and output type: the code of the other three combinations would only take up
+// instruction cache, which the softmax warps are short of)
+template <bool kSwa, bool kOutF32>
 __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_constant__ CUtensorMap tm_q,
                                                                   const __grid_constant__ CUtensorMap tm_k,
                                                                   const __grid_constant__ CUtensorMap tm_v,
@@ -639,13 +642,13 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             // unit's keys also end with the shard (k_end), before the causal limit of later queries
             const int k_end = klo + n_keys - 1;
             const int c_hi = min(qpos, k_end) - kbase;
-            const int c_lo = a.is_swa ? qpos - kHist - kbase : -(1 << 30);
+            const int c_lo = kSwa ? qpos - kHist - kbase : -(1 << 30);
             // Per 32-column chunk, for the whole Q tile: 0 = every row sees every key (no per-element mask),
             // 1 = mixed, 2 = no row sees any key.  Only the two ends of the band are mixed.
             auto chunk_kind = [&](int ch) {
                 const int key_lo = kbase + ch * 32, key_hi = key_lo + 31;
-                if (key_lo > qt_last || key_lo > k_end || (a.is_swa && key_hi < qt_first - kHist)) return 2;
-                if (key_hi <= qt_first && key_hi <= k_end && (!a.is_swa || key_lo >= qt_last - kHist)) return 0;
+                if (key_lo > qt_last || key_lo > k_end || (kSwa && key_hi < qt_first - kHist)) return 2;
+                if (key_hi <= qt_first && key_hi <= k_end && (!kSwa || key_lo >= qt_last - kHist)) return 0;
                 return 1;
             };
 
@@ -787,7 +790,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) k_prefill_attn(const __grid_c
             tc5::fence_after_sync();
             const bool partial = a.n_ksplit > 1 || a.cp_partial;
             const float inv_l = partial ? 1.0f : 1.0f / l;
-            const bool f32 = a.out_dtype == kDtypeF32;
+            constexpr bool f32 = kOutF32;
             const int row0 = un.t0 + w * kQPos + un.split * a.t_pad;  // row of the output tensor this Q tile starts at
             if (partial && un.t0 + w * kQPos + qi < a.n_tok)
                 a.part_ml[size_t(row0 + qi) * kNHead + kvh * kGqa + hl] = make_float2(m, l);
@@ -982,7 +985,11 @@ cudaError_t prefill_kernel_setup() {
     }
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-    return cudaFuncSetAttribute(k_prefill_attn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(k_prefill_attn<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_prefill_attn<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_prefill_attn<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(k_prefill_attn<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    return e;
 }
 
 void prefill_workspace_free(PrefillWorkspace &ws) {
@@ -1132,7 +1139,11 @@ cudaError_t launch_prefill(const PrefillParams &p, PrefillWorkspace &ws, cudaStr
         attr.val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = &attr;
         cfg.numAttrs = no_pdl ? 0 : 1;
-        e = cudaLaunchKernelEx(&cfg, k_prefill_attn, tm_q, tm_k, tm_v, tm_o, a);
+        const bool f32 = a.out_dtype == kDtypeF32;
+        if (a.is_swa) e = f32 ? cudaLaunchKernelEx(&cfg, k_prefill_attn<true, true>, tm_q, tm_k, tm_v, tm_o, a)
+                              : cudaLaunchKernelEx(&cfg, k_prefill_attn<true, false>, tm_q, tm_k, tm_v, tm_o, a);
+        else e = f32 ? cudaLaunchKernelEx(&cfg, k_prefill_attn<false, true>, tm_q, tm_k, tm_v, tm_o, a)
+                     : cudaLaunchKernelEx(&cfg, k_prefill_attn<false, false>, tm_q, tm_k, tm_v, tm_o, a);
     }
     if (e != cudaSuccess) return e;
     (*n_launches)++;
