@@ -36,7 +36,7 @@ L2_BYTES = 126 << 20
 # workload on this part: the decode kernel on 64 sequences x 8192 cached tokens, and the prefill attention kernel on
 # the 4000-token sliding-window prompt.  --traffic-from replaces the decode figure with one read from an ncu CSV.
 DECODE_NCU_DRAM_BYTES_PER_LAUNCH = 1082838000 + 4117760
-PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41037312 + 1722368
+PREFILL_NCU_DRAM_BYTES_PER_LAUNCH = 41030400 + 1144320
 DECODE_WORKLOAD = ("decode: 64 seqs x 8192 cached tokens, 1 full layer, 32q/4kv heads x 128, bf16 qkv rows, "
                    "fp16 KV cache, norm+RoPE+KV write fused")
 
