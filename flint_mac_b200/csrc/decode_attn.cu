@@ -646,7 +646,7 @@ constexpr size_t smem_bytes() {  // 1 KiB of slack for the 1024-byte alignment o
     return sizeof(DecSmem<kStages>) + 1024;
 }
 
-constexpr int kCapSmall = 76, kCapMid = 256;
+constexpr int kCapSmall = 76, kCapMid = 304;  // 304: one wave of items on a 148-SM part (two CTAs per SM) and a little more
 static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kCapSmall>) <= 4096, "small variant fits 4 KiB of parameters");
 static_assert(sizeof(DecParams) + sizeof(DecItemsParam<kMaxParamItems>) <= 32764, "largest variant fits the limit");
 
